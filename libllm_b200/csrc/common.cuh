@@ -1,0 +1,96 @@
+// Shared helpers of the sm_100a kernels: element types, status codes and the error
+// string each library keeps for its last failed call.
+//
+// Every exported function is `extern "C"`, takes raw device pointers plus the CUDA
+// stream to launch on, allocates nothing and returns 0 or a non-zero status; the Python
+// side (libllm_b200/csrc/ops.py) turns a status into an exception with this message.
+// The reference reports errors the same way at its C boundary: a code and a message
+// (src/libllm/llm.h:42-47).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define LLM_OK 0
+#define LLM_ERR_INVALID 0x0100
+#define LLM_ERR_CUDA 0x0102
+
+enum LlmDtype { LLM_F32 = 0, LLM_BF16 = 1 };
+
+static thread_local char g_llm_error[512] = "";
+
+#define LLM_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define LLM_FAIL(...)                                   \
+  do {                                                  \
+    snprintf(g_llm_error, sizeof(g_llm_error), __VA_ARGS__); \
+    return LLM_ERR_INVALID;                             \
+  } while (0)
+
+#define LLM_REQUIRE(cond, ...) \
+  do {                         \
+    if (!(cond)) LLM_FAIL(__VA_ARGS__); \
+  } while (0)
+
+#define LLM_CHECK_LAUNCH(name)                                                        \
+  do {                                                                                \
+    cudaError_t e_ = cudaGetLastError();                                              \
+    if (e_ != cudaSuccess) {                                                          \
+      snprintf(g_llm_error, sizeof(g_llm_error), "%s: %s", name, cudaGetErrorString(e_)); \
+      return LLM_ERR_CUDA;                                                            \
+    }                                                                                 \
+  } while (0)
+
+#define LLM_CHECK_CUDA(expr, name)                                                    \
+  do {                                                                                \
+    cudaError_t e_ = (expr);                                                          \
+    if (e_ != cudaSuccess) {                                                          \
+      snprintf(g_llm_error, sizeof(g_llm_error), "%s: %s", name, cudaGetErrorString(e_)); \
+      return LLM_ERR_CUDA;                                                            \
+    }                                                                                 \
+  } while (0)
+
+#define LLM_DEFINE_LAST_ERROR(fn) \
+  LLM_EXPORT const char *fn() { return g_llm_error; }
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block with a fixed order of additions: warps first, then the warp totals
+// in warp order.  The result does not depend on how many rows the launch has.
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float *scratch /* THREADS/32 + 1 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < THREADS / 32 ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[THREADS / 32] = t;
+  }
+  __syncthreads();
+  return scratch[THREADS / 32];
+}

@@ -1,0 +1,142 @@
+// Embedding gather, residual-add + RMSNorm, and SwiGLU.  Element type T is float (the
+// true 32-bit path) or bfloat16; all arithmetic is in 32-bit.
+//
+// Reference counterparts: lookup (src/flint/cuda/lookup.cu:30-43), rmsNorm
+// (src/flint/cuda/rms_norm.cu:31-84) followed by a separate add
+// (src/flint/cuda/binary.cu:48-88), swiglu (src/flint/cuda/swiglu.cu:29-59).  Here the
+// residual stream is kept in 32-bit and the add is part of the norm kernel, so one
+// pass over the row does what three launches do there.
+#include "common.cuh"
+
+LLM_DEFINE_LAST_ERROR(llm_elementwise_last_error)
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const T *__restrict__ table, const int *__restrict__ tokens,
+                                 float *__restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  // Token ids are checked on the host before they are uploaded; ids that the sampler
+  // wrote on the device are below the vocabulary size by construction.  The clamp keeps
+  // the read inside the table whatever happens.
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const T *row = table + (size_t)id * hidden;
+  float *o = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, float *out,
+                             int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
+  int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == LLM_F32)
+    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>((const float *)table, tokens, out, hidden, vocab);
+  else if (dtype == LLM_BF16)
+    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16 *)table, tokens, out, hidden, vocab);
+  else
+    LLM_FAIL("embedding: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("embedding");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- add + rmsnorm
+// For each output row i (source row r = rows ? rows[i] : i):
+//   v = resid[r] + sum_p delta[p][r]      (32-bit; parts added in index order)
+//   if (!rows) resid[r] = v               (the residual stream moves on)
+//   out[i] = v * w * rsqrt(mean(v^2) + eps)   (skipped when out is null)
+template <typename TD, typename TO, int THREADS>
+__global__ void add_rmsnorm_kernel(float *__restrict__ resid, const TD *__restrict__ delta,
+                                   int n_parts, size_t part_stride, const float *__restrict__ weight,
+                                   float eps, TO *__restrict__ out, const int *__restrict__ rows,
+                                   int hidden) {
+  extern __shared__ float row_buf[];   // hidden floats
+  __shared__ float scratch[THREADS / 32 + 1];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float *x = resid + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    float v = x[c];
+    for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + (size_t)r * hidden + c]);
+    row_buf[c] = v;
+    if (!rows && n_parts > 0) x[c] = v;
+    ss += v * v;
+  }
+  if (!out) return;
+  const float total = block_sum<THREADS>(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  TO *o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) o[c] = from_float<TO>(row_buf[c] * weight[c] * inv);
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size_t part_stride,
+                              const float *weight, float eps, void *out, const int *rows, int n_rows,
+                              int hidden, cudaStream_t stream) {
+  constexpr int THREADS = 256;
+  size_t smem = (size_t)hidden * sizeof(float);
+  auto kern = add_rmsnorm_kernel<TD, TO, THREADS>;
+  if (smem > 48 * 1024) {
+    LLM_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: a row of %d values does not fit shared memory", hidden);
+    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   "add_rmsnorm attribute");
+  }
+  kern<<<n_rows, THREADS, smem, stream>>>(resid, (const TD *)delta, n_parts, part_stride, weight, eps,
+                                          (TO *)out, rows, hidden);
+  LLM_CHECK_LAUNCH("add_rmsnorm");
+  return LLM_OK;
+}
+
+// delta_dtype: type of delta; out_dtype: type of out.  delta may be null (n_parts 0),
+// out may be null (add only), rows may be null (all rows, residual written back).
+LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype, int n_parts,
+                               long long part_stride, const float *weight, float eps, void *out,
+                               int out_dtype, const int *rows, int n_rows, int hidden,
+                               cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 0, "add_rmsnorm: bad sizes");
+  LLM_REQUIRE(out == nullptr || weight != nullptr, "add_rmsnorm: a norm needs its weight");
+  if (!delta) n_parts = 0;
+  if (delta_dtype == LLM_F32 && out_dtype == LLM_F32)
+    return launch_add_rmsnorm<float, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+  if (delta_dtype == LLM_F32 && out_dtype == LLM_BF16)
+    return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+  if (delta_dtype == LLM_BF16 && out_dtype == LLM_BF16)
+    return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+  if (delta_dtype == LLM_BF16 && out_dtype == LLM_F32)
+    return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+  LLM_FAIL("add_rmsnorm: unknown dtypes %d, %d", delta_dtype, out_dtype);
+}
+
+// ---------------------------------------------------------------- swiglu
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(a) = a / (1 + exp(-a)).
+template <typename T>
+__global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, int inter, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_float(gu[t * 2 * inter + i]);
+    const float u = to_float(gu[t * 2 * inter + inter + i]);
+    out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+LLM_EXPORT int llm_swiglu(int dtype, const void *gu, void *out, int n_tokens, int inter,
+                          cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
+  const size_t total = (size_t)n_tokens * inter;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == LLM_F32)
+    swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float *)gu, (float *)out, inter, total);
+  else if (dtype == LLM_BF16)
+    swiglu_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, inter, total);
+  else
+    LLM_FAIL("swiglu: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("swiglu");
+  return LLM_OK;
+}

@@ -1,0 +1,201 @@
+"""Python faces of the CUDA kernels: each takes torch tensors on a CUDA device, checks
+what the kernel relies on (device, type, contiguity, alignment) and launches on the
+current stream.  Nothing here computes on the host or falls back to torch operators:
+a tensor that is not on a CUDA device is an error."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from ..errors import ExtensionError, UnsupportedError
+from . import build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise UnsupportedError(f"element type {dt} is not supported (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _on_gpu(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ExtensionError("libllm_b200 kernels run on a CUDA device only; got a tensor on "
+                                 f"'{t.device}' (there is no CPU fallback)")
+
+
+_protos = {}
+
+
+def _fn(family: str, name: str, argtypes):
+    key = (family, name)
+    f = _protos.get(key)
+    if f is None:
+        lib = build.load(family)
+        f = getattr(lib, name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        err = getattr(lib, f"llm_{family}_last_error")
+        err.restype = ctypes.c_char_p
+        _protos[key] = f = (f, err)
+    return f
+
+
+def _call(family: str, name: str, argtypes, *args) -> None:
+    f, err = _fn(family, name, argtypes)
+    status = f(*args)
+    if status != 0:
+        msg = err().decode("utf-8", "replace")
+        if status == 0x0100:
+            raise UnsupportedError(msg)
+        raise ExtensionError(f"{name} failed (status {status:#x}): {msg}")
+
+
+# ------------------------------------------------------------------ elementwise
+def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = float(table[tokens[t], :]); out is the 32-bit residual stream."""
+    _on_gpu(table, tokens, out)
+    n = tokens.numel()
+    assert tokens.dtype == torch.int32 and out.dtype == torch.float32
+    assert table.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n, table.shape[1])
+    _call("elementwise", "llm_embedding",
+          [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+          dtype_code(table.dtype), _ptr(table), _ptr(tokens), _ptr(out), n, table.shape[1], table.shape[0],
+          _stream())
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> None:
+    """resid += sum of delta's parts (32-bit, written back unless ``rows`` selects a
+    subset), then out = rmsnorm(resid) * weight.  ``delta`` is [T, H] or [parts, T, H]."""
+    _on_gpu(resid, delta, weight, out, rows)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.dim() == 2
+    T, H = resid.shape
+    n_parts, stride, ddt = 0, 0, F32
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == resid.shape
+        n_parts = 1 if delta.dim() == 2 else delta.shape[0]
+        stride = T * H
+        ddt = dtype_code(delta.dtype)
+    n_rows = T if rows is None else rows.numel()
+    odt = F32
+    if out is not None:
+        assert weight is not None and weight.dtype == torch.float32 and weight.numel() == H
+        assert out.is_contiguous() and tuple(out.shape) == (n_rows, H)
+        odt = dtype_code(out.dtype)
+    if rows is not None:
+        assert rows.dtype == torch.int32
+    _call("elementwise", "llm_add_rmsnorm",
+          [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p,
+           c_int, c_int, c_void_p],
+          _ptr(resid), _ptr(delta), ddt, n_parts, stride, _ptr(weight), float(eps), _ptr(out), odt,
+          _ptr(rows), n_rows, H, _stream())
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gu[t, i]) * gu[t, I + i]."""
+    _on_gpu(gu, out)
+    T, two_i = gu.shape
+    assert gu.is_contiguous() and out.is_contiguous() and out.dtype == gu.dtype
+    assert tuple(out.shape) == (T, two_i // 2)
+    _call("elementwise", "llm_swiglu", [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(gu.dtype), _ptr(gu), _ptr(out), T, two_i // 2, _stream())
+    return out
+
+
+# ------------------------------------------------------------------ plain matrix product
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+               bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T (+ bias) on the CUDA cores, 32-bit accumulate."""
+    _on_gpu(a, w, out, bias)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and tuple(out.shape) == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and a.dtype == w.dtype
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    _call("gemm_plain", "llm_gemm_plain",
+          [c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+           c_int, c_int, c_int, c_void_p],
+          dtype_code(a.dtype), dtype_code(out.dtype), _ptr(a), a.stride(0) if M > 1 else K, _ptr(w),
+          w.stride(0), _ptr(bias), _ptr(out), out.stride(0) if M > 1 else N, M, N, K, _stream())
+    return out
+
+
+# ------------------------------------------------------------------ rope + cache write
+def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, table: torch.Tensor,
+                     tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
+                     kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], page_size: int,
+                     write_cache: bool = True) -> None:
+    """Rotates the q and k heads of the stacked rows in place and appends k and v to the
+    paged cache [pages, kv_heads, page_size, d] of one layer."""
+    _on_gpu(qkv, table, tok_seq, tok_pos, page_table, kcache, vcache)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.dim() == 2
+    assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
+    if write_cache:
+        assert kcache.dtype == qkv.dtype and kcache.is_contiguous() and vcache.is_contiguous()
+        assert tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
+    _call("rope", "llm_rope_cache_write",
+          [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), T, n_heads, n_kv, head_dim, _ptr(table),
+          table.shape[0], table.shape[1], _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table),
+          page_table.stride(0), _ptr(kcache), _ptr(vcache), page_size, 1 if write_cache else 0, _stream())
+
+
+# ------------------------------------------------------------------ attention (generic)
+def attention_generic(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                      tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
+                      n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
+                      scale: float) -> torch.Tensor:
+    """q is a [T, >= n_heads*d] view whose first n_heads*d columns are the rotated queries."""
+    _on_gpu(q, out, kcache, vcache, tok_seq, tok_pos, page_table)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T and out.shape[1] == n_heads * head_dim
+    assert kcache.dtype == q.dtype and out.dtype == q.dtype
+    _call("attention_generic", "llm_attention_generic",
+          [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+          dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), T, n_heads, n_kv, head_dim,
+          page_size, int(window or 0), float(scale), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _on_gpu(logits, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    _call("sampling", "llm_argmax", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+          _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out), _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, uniforms: torch.Tensor,
+           out: torch.Tensor) -> torch.Tensor:
+    _on_gpu(logits, uniforms, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert uniforms.dtype == torch.float32 and uniforms.numel() >= logits.shape[0]
+    _call("sampling", "llm_sample",
+          [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
+          _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], float(temperature), int(top_k),
+          float(top_p), _ptr(uniforms), _ptr(out), _stream())
+    return out

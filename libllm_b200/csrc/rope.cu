@@ -1,0 +1,83 @@
+// Rotary position encoding of q and k and the append of k and v to the paged cache,
+// in one pass over the stacked q|k|v rows of a step.
+//
+// The reference rotates with about fourteen elementwise launches per layer
+// (src/libllm/llama.cc:151-176) and appends by re-allocating and copying the whole
+// cache (src/libllm/llama.cc:203-212, src/flint/functional.cc:126-144).  The rotation
+// pairs element i with i + d/2 (src/libllm/llama.cc:151-164):
+//   out[i]       = x[i] * cos - x[i + d/2] * sin
+//   out[i + d/2] = x[i + d/2] * cos + x[i] * sin
+// cos and sin come from a 32-bit table [positions, d] (d/2 cosines, then d/2 sines) that
+// is computed in 64-bit on the host side; the arithmetic here is 32-bit, rounded once.
+//
+// Cache layout per layer: [pages, kv_heads, page_size, d]; a token at position p of a
+// sequence lies in page page_table[seq][p / page_size] at row p % page_size.
+#include "common.cuh"
+
+LLM_DEFINE_LAST_ERROR(llm_rope_last_error)
+
+template <typename T>
+__global__ void rope_cache_write_kernel(T *__restrict__ qkv, long long row_stride, int n_heads,
+                                        int n_kv, int d, const float *__restrict__ table,
+                                        int table_rows, int rot_dim, const int *__restrict__ tok_seq,
+                                        const int *__restrict__ tok_pos, const int *__restrict__ page_table,
+                                        int pt_stride, T *__restrict__ kcache, T *__restrict__ vcache,
+                                        int page_size, int write_cache) {
+  const int t = blockIdx.x;
+  const int slot = blockIdx.y;                 // 0..n_heads-1: q, then k heads, then v heads
+  const int pos = tok_pos[t];
+  T *row = qkv + (size_t)t * row_stride + (size_t)slot * d;
+  const int half = rot_dim / 2;
+  const bool is_v = slot >= n_heads + n_kv;
+  const bool is_k = !is_v && slot >= n_heads;
+  T *dst = nullptr;
+  if ((is_k || is_v) && write_cache) {
+    const int kvh = is_k ? slot - n_heads : slot - n_heads - n_kv;
+    const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+    T *base = is_k ? kcache : vcache;
+    dst = base + (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * d;
+  }
+  if (is_v) {
+    if (dst)
+      for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = row[i];
+    return;
+  }
+  const int p = pos < table_rows ? pos : table_rows - 1;   // the host refuses longer sequences
+  const float *cs = table + (size_t)p * rot_dim;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float c = cs[i], s = cs[half + i];
+    const float a = to_float(row[i]), b = to_float(row[i + half]);
+    const T ra = from_float<T>(a * c - b * s);
+    const T rb = from_float<T>(b * c + a * s);
+    if (is_k) {
+      if (dst) { dst[i] = ra; dst[i + half] = rb; }
+      row[i] = ra; row[i + half] = rb;
+    } else {
+      row[i] = ra; row[i + half] = rb;
+    }
+  }
+  // Channels beyond the rotated ones (rot_dim < d) pass through unchanged.
+  if (is_k && dst)
+    for (int i = rot_dim + threadIdx.x; i < d; i += blockDim.x) dst[i] = row[i];
+}
+
+LLM_EXPORT int llm_rope_cache_write(int dtype, void *qkv, long long row_stride, int n_tokens, int n_heads,
+                                    int n_kv, int d, const float *table, int table_rows, int rot_dim,
+                                    const int *tok_seq, const int *tok_pos, const int *page_table,
+                                    int pt_stride, void *kcache, void *vcache, int page_size,
+                                    int write_cache, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0, "rope: bad sizes");
+  LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim > 0, "rope: rotated width %d does not fit head size %d", rot_dim, d);
+  LLM_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope: too many heads for one launch");
+  dim3 grid(n_tokens, n_heads + 2 * n_kv);
+  int threads = d / 2 >= 64 ? 64 : 32;
+  if (dtype == LLM_F32)
+    rope_cache_write_kernel<float><<<grid, threads, 0, stream>>>((float *)qkv, row_stride, n_heads, n_kv, d, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride, (float *)kcache, (float *)vcache, page_size, write_cache);
+  else if (dtype == LLM_BF16)
+    rope_cache_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16 *)qkv, row_stride, n_heads, n_kv, d, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride, (__nv_bfloat16 *)kcache, (__nv_bfloat16 *)vcache, page_size, write_cache);
+  else
+    LLM_FAIL("rope: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("rope_cache_write");
+  return LLM_OK;
+}

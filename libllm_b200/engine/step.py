@@ -1,0 +1,361 @@
+"""The step function: a batch of sequences, each bringing its next tokens (a whole
+prompt, a piece of one, or a single token), run as one batch from the cache.
+
+The reference has two entry points for one sequence, ``prefill`` and ``decode``
+(src/libllm/model_for_generation.h:62-69, src/libllm/llama.cc:349-368), and a
+rectangular batch inside the model.  Here one function takes ragged batches: the
+tokens of all sequences lie one after another, per-token arrays say which sequence and
+position each belongs to, and the kernels index the paged cache with them.  Only the
+tokens given are computed; padding does not exist.
+
+Steps in which every sequence brings one token are captured once per batch shape as a
+CUDA graph and replayed; the step's descriptor (tokens, positions, page tables) is
+copied into the graph's fixed buffer before each replay."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import KVCache
+from ..csrc import ops
+from ..errors import CacheError, InvalidArgError
+from ..parts.base import StepContext
+from .model import Model
+
+
+@dataclass
+class StepItem:
+    """One sequence's share of a step: its slot, its next tokens, and the places among
+    these tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    """temperature 0 is greedy; top_k 0 draws from the whole vocabulary.  The defaults
+    are the reference's (src/libllm/llm.cc:125-132)."""
+    temperature: float = 1.0
+    top_k: int = 50
+    top_p: float = 0.8
+
+    def validate(self) -> None:
+        if self.temperature < 0:
+            raise InvalidArgError("temperature must not be negative")
+        if not 0 <= self.top_k <= 1024:
+            raise InvalidArgError("top_k must lie in 0..1024 (0: the whole vocabulary)")
+        if not self.top_p > 0:
+            raise InvalidArgError("top_p must be positive")
+        if self.top_k == 0 and self.top_p < 1.0 and self.temperature > 0:
+            raise InvalidArgError("top_p below 1 needs a top_k")
+
+
+GREEDY = SamplingParams(temperature=0.0, top_k=1, top_p=1.0)
+
+
+@dataclass
+class _Piece:
+    """Part of one item that runs in one launch sequence."""
+    index: int          # index of the item in the step
+    slot: int
+    start: int          # offset into the item's tokens
+    count: int
+    past: int           # tokens cached before this piece
+
+
+class _Descriptor:
+    """Host staging and device copy of one step's integer arrays."""
+
+    def __init__(self, device, n_tokens: int, n_seqs: int, n_want: int, widths: List[int]):
+        self.n_tokens, self.n_seqs, self.n_want, self.widths = n_tokens, n_seqs, n_want, widths
+        T, B, W = n_tokens, n_seqs, n_want
+        sizes = [T, T, T, B + 1, B, B, W, B] + [B * w for w in widths]
+        self.offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(int)
+        total = int(self.offsets[-1])
+        self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self.host.zero_()
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        self.copied = torch.cuda.Event()
+        self._pending = False
+        self._sizes = sizes
+
+    def field(self, i: int, dev: bool = False):
+        a, n = int(self.offsets[i]), self._sizes[i]
+        return (self.dev if dev else self.np)[a:a + n]
+
+    def wait_host_free(self) -> None:
+        if self._pending:
+            self.copied.synchronize()
+            self._pending = False
+
+    def upload(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self._pending = True
+
+
+class Engine:
+    def __init__(self, model: Model, max_tokens: int, max_seq_len: Optional[int] = None,
+                 max_slots: Optional[int] = None, max_step_tokens: int = 8192, page_size: int = 64,
+                 use_graphs: bool = True):
+        """``max_tokens``: tokens all live sequences may hold together (each sequence's
+        count rounded up to a multiple of ``page_size``); it sizes the cache."""
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.page_size = page_size
+        n_pages = (max_tokens + page_size - 1) // page_size
+        self.max_seq_len = min(max_seq_len or model.max_positions, model.max_positions, n_pages * page_size)
+        self.max_step_tokens = max(1, max_step_tokens)
+        self.use_graphs = use_graphs
+        self.cache = KVCache(model.run_cache_needs(), model.run_state_needs(), max_tokens, self.dtype,
+                             self.device, page_size, max_slots)
+        self.vocab = model.spec.vocab_size
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self._eager_desc: Dict[tuple, _Descriptor] = {}
+        self.launch_log: Optional[List[str]] = None
+        self.steps_run = 0
+
+    # ---------------------------------------------------------------- sequences
+    def open_sequence(self) -> int:
+        return self.cache.open()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def sequence_length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---------------------------------------------------------------- the step
+    def step(self, items: Sequence[StepItem], sampling: Optional[SamplingParams] = None,
+             uniforms: Optional[Sequence[float]] = None, return_logits: bool = True):
+        """Runs the items' tokens and returns the logits at the wanted places, a 32-bit
+        device tensor [wanted, vocab] in the order of the items and of their ``want``.
+        With ``sampling`` it returns (logits or None, tokens): a token drawn at each
+        wanted place (int32 on the device); ``uniforms`` then holds one number in [0, 1)
+        per wanted place."""
+        items = list(items)
+        if not items:
+            raise InvalidArgError("a step needs at least one sequence")
+        self._validate(items)
+        n_want = sum(len(it.want) for it in items)
+        if sampling is not None:
+            sampling.validate()
+            if uniforms is None:
+                uniforms = [0.0] * n_want
+            if len(uniforms) != n_want:
+                raise InvalidArgError("one uniform number per wanted place is needed")
+        # Pages first: either the whole step fits the cache or nothing changes.
+        self.cache.reserve({it.slot: self.cache.length(it.slot) + len(it.tokens) for it in items})
+
+        decode_only = all(len(it.tokens) == 1 for it in items)
+        if decode_only and self.use_graphs and len(items) <= self.max_step_tokens:
+            out = self._run_decode_graph(items, sampling, uniforms, return_logits)
+        else:
+            out = self._run_eager(items, sampling, uniforms, return_logits)
+        self.steps_run += 1
+        return out
+
+    def _validate(self, items: Sequence[StepItem]) -> None:
+        seen = set()
+        for it in items:
+            if it.slot in seen:
+                raise InvalidArgError(f"slot {it.slot} appears twice in one step")
+            seen.add(it.slot)
+            n = len(it.tokens)
+            if n == 0:
+                raise InvalidArgError(f"slot {it.slot}: a sequence in a step brings at least one token")
+            past = self.cache.length(it.slot)       # raises if the slot is not open
+            if past + n > self.max_seq_len:
+                raise InvalidArgError(f"slot {it.slot}: {past} + {n} tokens exceed the longest sequence "
+                                      f"this engine holds ({self.max_seq_len})")
+            for t in it.tokens:
+                if not 0 <= int(t) < self.vocab:
+                    raise InvalidArgError(f"slot {it.slot}: token id {t} outside the vocabulary ({self.vocab})")
+            for w in it.want:
+                if not 0 <= int(w) < n:
+                    raise InvalidArgError(f"slot {it.slot}: wanted place {w} outside the {n} tokens given")
+
+    # ---------------------------------------------------------------- descriptor
+    def _fill(self, desc: _Descriptor, pieces: List[_Piece], items: Sequence[StepItem],
+              want_rows: List[int], uniforms: Optional[Sequence[float]]) -> None:
+        desc.wait_host_free()
+        tokens, tok_seq, tok_pos = desc.field(0), desc.field(1), desc.field(2)
+        seq_start, seq_past, seq_slot = desc.field(3), desc.field(4), desc.field(5)
+        want, uni = desc.field(6), desc.field(7)
+        o = 0
+        for b, p in enumerate(pieces):
+            toks = items[p.index].tokens[p.start:p.start + p.count]
+            tokens[o:o + p.count] = toks
+            tok_seq[o:o + p.count] = b
+            tok_pos[o:o + p.count] = np.arange(p.past + p.start, p.past + p.start + p.count)
+            seq_start[b] = o
+            seq_past[b] = p.past + p.start
+            seq_slot[b] = p.slot
+            o += p.count
+        seq_start[len(pieces)] = o
+        want[:len(want_rows)] = want_rows
+        if uniforms is not None:
+            uni.view(np.float32)[:len(uniforms)] = np.asarray(uniforms, dtype=np.float32)
+        slots = [p.slot for p in pieces]
+        for g, w in enumerate(desc.widths):
+            desc.field(8 + g).reshape(len(pieces), w)[:] = self.cache.page_table(g, slots, w)
+        desc.upload()
+
+    def _context(self, desc: _Descriptor, pieces: List[_Piece], n_want: int, decode_only: bool,
+                 max_kv_len: int) -> Tuple[StepContext, List[torch.Tensor]]:
+        B = len(pieces)
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, n_tokens=desc.n_tokens, n_seqs=B,
+            tokens=desc.field(0, True), tok_seq=desc.field(1, True), tok_pos=desc.field(2, True),
+            seq_start=desc.field(3, True), seq_past=desc.field(4, True), seq_slot=desc.field(5, True),
+            want_rows=desc.field(6, True)[:n_want], q_lens=[p.count for p in pieces],
+            past_lens=[p.past + p.start for p in pieces], slots=[p.slot for p in pieces],
+            max_q_len=max(p.count for p in pieces), max_kv_len=max_kv_len, decode_only=decode_only)
+        ctx.extras["uniforms"] = desc.field(7, True).view(torch.float32)
+        tables = [desc.field(8 + g, True).view(B, w) for g, w in enumerate(desc.widths)]
+        return ctx, tables
+
+    def _sample(self, logits: torch.Tensor, sampling: SamplingParams, uniforms: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        if sampling.temperature == 0:
+            return ops.argmax(logits, out)
+        return ops.sample(logits, sampling.temperature, sampling.top_k, sampling.top_p, uniforms, out)
+
+    # ---------------------------------------------------------------- eager path (prompts, mixed steps)
+    def _run_eager(self, items, sampling, uniforms, return_logits):
+        pieces_all: List[List[_Piece]] = [[]]
+        room = self.max_step_tokens
+        for i, it in enumerate(items):
+            past = self.cache.length(it.slot)
+            start, n = 0, len(it.tokens)
+            while start < n:
+                if room == 0:
+                    pieces_all.append([])
+                    room = self.max_step_tokens
+                c = min(room, n - start)
+                pieces_all[-1].append(_Piece(i, it.slot, start, c, past))
+                start += c
+                room -= c
+        logits_parts, token_parts = [], []
+        want_base = np.cumsum([0] + [len(it.want) for it in items])
+        order: List[int] = []          # index into the flat wanted list, in the order computed
+        for pieces in pieces_all:
+            T = sum(p.count for p in pieces)
+            want_rows, uni = [], []
+            o = 0
+            for p in pieces:
+                for j, w in enumerate(items[p.index].want):
+                    if p.start <= w < p.start + p.count:
+                        want_rows.append(o + w - p.start)
+                        order.append(int(want_base[p.index]) + j)
+                        if uniforms is not None:
+                            uni.append(uniforms[int(want_base[p.index]) + j])
+                o += p.count
+            widths = [self._table_width(pieces)] * len(self.cache.groups)
+            desc = _Descriptor(self.device, T, len(pieces), len(want_rows), widths)
+            self._fill(desc, pieces, items, want_rows, uni if uniforms is not None else None)
+            max_kv = max(p.past + p.start + p.count for p in pieces)
+            ctx, tables = self._context(desc, pieces, len(want_rows), all(p.count == 1 for p in pieces), max_kv)
+            logits = self.model.forward(ctx, self.cache, tables)
+            if sampling is not None and len(want_rows):
+                token_parts.append(self._sample(logits, sampling, ctx.extras["uniforms"]))
+            if return_logits or sampling is None:
+                logits_parts.append(logits)
+            for p in pieces:
+                self.cache.commit(p.slot, p.past + p.start + p.count)
+            desc.wait_host_free()
+        perm = None
+        if order != sorted(order):
+            perm = torch.tensor(np.argsort(order), device=self.device)
+        logits = None
+        if logits_parts:
+            logits = logits_parts[0] if len(logits_parts) == 1 else torch.cat(logits_parts, 0)
+            if perm is not None:
+                logits = logits[perm]
+        if sampling is None:
+            return logits
+        if token_parts:
+            tokens = token_parts[0] if len(token_parts) == 1 else torch.cat(token_parts, 0)
+        else:
+            tokens = torch.empty(0, dtype=torch.int32, device=self.device)
+        if perm is not None:
+            tokens = tokens[perm]
+        return (logits if return_logits else None), tokens
+
+    def _table_width(self, pieces: List[_Piece]) -> int:
+        need = max((p.past + p.start + p.count + self.page_size - 1) // self.page_size for p in pieces)
+        return max(8, (need + 7) // 8 * 8)
+
+    # ---------------------------------------------------------------- graph path (one token each)
+    def _run_decode_graph(self, items, sampling, uniforms, return_logits):
+        B = len(items)
+        pieces = [_Piece(i, it.slot, 0, 1, self.cache.length(it.slot)) for i, it in enumerate(items)]
+        need_pages = max((p.past + 1 + self.page_size - 1) // self.page_size for p in pieces)
+        width = 8
+        while width < need_pages:
+            width *= 2
+        key = (B, width, sampling)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = _DecodeGraph(self, B, width, sampling)
+            self._graphs[key] = graph
+        # Logits are computed for every sequence; the wanted ones are picked afterwards.
+        rows = [i for i, it in enumerate(items) if len(it.want)]
+        uni_full = None
+        if sampling is not None:
+            uni_full = [0.0] * B
+            for r, u in zip(rows, uniforms):
+                uni_full[r] = u
+        self._fill(graph.desc, pieces, items, list(range(B)), uni_full)
+        graph.run()
+        for p in pieces:
+            self.cache.commit(p.slot, p.past + 1)
+        pick = None if len(rows) == B else torch.tensor(rows, device=self.device, dtype=torch.long)
+        logits = graph.logits if pick is None else graph.logits[pick]
+        if sampling is None:
+            return logits
+        tokens = graph.tokens if pick is None else graph.tokens[pick]
+        return (logits if return_logits else None), tokens
+
+
+class _DecodeGraph:
+    """A captured step of B sequences bringing one token each, page tables ``width`` wide."""
+
+    def __init__(self, engine: Engine, B: int, width: int, sampling: Optional[SamplingParams]):
+        self.engine, self.B, self.width, self.sampling = engine, B, width, sampling
+        self.desc = _Descriptor(engine.device, B, B, B, [width] * len(engine.cache.groups))
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.tokens: Optional[torch.Tensor] = None
+
+    def _body(self):
+        eng = self.engine
+        pieces = [_Piece(i, 0, 0, 1, 0) for i in range(self.B)]
+        ctx, tables = eng._context(self.desc, pieces, self.B, True, self.width * eng.page_size)
+        logits = eng.model.forward(ctx, eng.cache, tables)
+        tokens = None
+        if self.sampling is not None:
+            tokens = eng._sample(logits, self.sampling, ctx.extras["uniforms"])
+        return logits, tokens
+
+    def run(self) -> None:
+        if self.graph is None:
+            # First use: run once outside capture (loads kernels, sizes library
+            # workspaces), then capture the same launches.  Both read the descriptor the
+            # caller has just uploaded, so the cache ends up with the same contents.
+            side = torch.cuda.Stream(device=self.engine.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._body()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits, self.tokens = self._body()
+        self.graph.replay()

@@ -1,0 +1,138 @@
+"""The engine against the plain implementation, in float32 and bfloat16, for every way of
+cutting the work: whole requests, the last 32 tokens one by one, batches of unequal
+lengths whose shorter requests end earlier with slots used again, long decoding, and the
+first tokens of a sequence."""
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import TINY, check_logits, model_folder, plain_weights, tokens_for
+from replay import replay_batch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+_cache = {}
+
+
+def setup(name, dtype, max_tokens=4096, **kw):
+    from libllm_b200.engine import Engine, Model
+    key = (name, dtype, max_tokens, tuple(sorted(kw.items())))
+    if key not in _cache:
+        folder = model_folder(name)
+        model = Model.from_folder(folder, dtype=dtype, device="cuda:0")
+        _cache[key] = (Engine(model, max_tokens=max_tokens, **kw), P.read_config(folder), plain_weights(folder))
+    return _cache[key]
+
+
+def plain(c, w, toks):
+    return P.forward_logits(c, w, toks)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_request_alone_and_whole(name, dtype):
+    engine, c, w = setup(name, dtype)
+    for i, n in enumerate([1, 2, 5, 33, 64, 65, 131]):
+        toks = tokens_for(name, n, i)
+        got = replay_batch(engine, [("r", toks, n)])["r"]
+        check_logits(got, plain(c, w, toks), dtype, f"{name} whole len {n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(name, dtype):
+    engine, c, w = setup(name, dtype)
+    for i, n in enumerate([33, 100, 160]):
+        toks = tokens_for(name, n, 10 + i)
+        got = replay_batch(engine, [("r", toks, n - 32)])["r"]
+        check_logits(got, plain(c, w, toks), dtype, f"{name} last-32 len {n}")
+
+
+WORKLOADS = {
+    # (prompt lengths, decoded tokens): the two tiny workloads of the benchmark description
+    "A": ([5, 9, 12], 8),
+    "B": ([1, 7, 33, 70], 16),
+    "C": ([3, 64, 17], 5),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_one_after_another(name, dtype):
+    """Three batches on a cache that holds only one of them at a time: slots and pages
+    are used again.  Requests decode different numbers of tokens, so some end earlier."""
+    prompts, n_dec = WORKLOADS[name]
+    cap = sum((p + n_dec + len(prompts) + 63) // 64 * 64 for p in prompts)
+    engine, c, w = setup(name, dtype, max_tokens=cap)
+    for b in range(3):
+        reqs = []
+        for j, p in enumerate(prompts):
+            total = p + n_dec - (j if b % 2 == 0 else len(prompts) - 1 - j)   # unequal ends
+            reqs.append((f"b{b}r{j}", tokens_for(name, total, 100 * b + j), p))
+        got = replay_batch(engine, reqs)
+        for rid, toks, _ in reqs:
+            check_logits(got[rid], plain(c, w, toks), dtype, f"{name} batch {b} {rid}")
+    assert engine.cache.groups[0].pool.in_use == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype):
+    """One token a step for 300 steps after a one-token prompt: crosses several pages."""
+    engine, c, w = setup("B", dtype)
+    toks = tokens_for("B", 300, 77)
+    got = replay_batch(engine, [("r", toks, 1)])["r"]
+    check_logits(got, plain(c, w, toks), dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(dtype):
+    """Positions 0, 1, 2 of short sequences, alone and beside a long neighbour."""
+    engine, c, w = setup("A", dtype)
+    short = tokens_for("A", 3, 5)
+    long_ = tokens_for("A", 90, 6)
+    alone = replay_batch(engine, [("s", short, 1)])["s"]
+    both = replay_batch(engine, [("l", long_, 60), ("s", short, 1)])
+    ref = plain(c, w, short)
+    check_logits(alone, ref, dtype, "first tokens alone")
+    check_logits(both["s"], ref, dtype, "first tokens beside a long request")
+    check_logits(both["l"], plain(c, w, long_), dtype, "long neighbour")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_cut_into_chunks(dtype):
+    """A step with more tokens than one launch sequence takes is cut inside a prompt."""
+    engine, c, w = setup("C", dtype, max_step_tokens=48)
+    reqs = [("a", tokens_for("C", 100, 1), 100), ("b", tokens_for("C", 30, 2), 30)]
+    got = replay_batch(engine, reqs)
+    for rid, toks, _ in reqs:
+        check_logits(got[rid], plain(c, w, toks), dtype, f"chunked {rid}")
+
+
+def test_batch_composition_does_not_change_float32_results():
+    """The same request alone and in a batch: float32 logits agree to rounding."""
+    engine, c, w = setup("B", "float32")
+    t0, t1, t2 = (tokens_for("B", n, 40 + n) for n in (50, 7, 90))
+    alone = replay_batch(engine, [("x", t0, 40)])["x"]
+    batch = replay_batch(engine, [("y", t1, 3), ("x", t0, 40), ("z", t2, 80)])["x"]
+    assert float((alone - batch).abs().max()) <= 1e-6 * float(alone.abs().mean()) + 1e-7
+
+
+def test_errors_leave_the_cache_unchanged():
+    from libllm_b200.engine import StepItem
+    from libllm_b200.errors import CacheError, InvalidArgError
+    engine, c, w = setup("A", "float32", max_tokens=128)
+    s = engine.open_sequence()
+    with pytest.raises(InvalidArgError):
+        engine.step([StepItem(s, [1, 2, 999], [0])])           # token outside the vocabulary
+    with pytest.raises(InvalidArgError):
+        engine.step([StepItem(s, [1, 2], [5])])                # wanted place outside the tokens
+    s2 = engine.open_sequence()
+    with pytest.raises(CacheError):
+        engine.step([StepItem(s, [1] * 100, []), StepItem(s2, [1] * 100, [])])   # 4 pages wanted, 2 exist
+    assert engine.cache.groups[0].pool.in_use == 0
+    engine.cache.check()
+    engine.close_sequence(s)
+    engine.close_sequence(s2)
+    with pytest.raises(CacheError):
+        engine.close_sequence(s2)

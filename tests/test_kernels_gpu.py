@@ -1,0 +1,255 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-6, "bfloat16": 1e-2}
+
+
+def close(got, ref, dtype, scale=None):
+    ref = ref.to(torch.float64)
+    err = float((got.detach().to(torch.float64).cpu() - ref.cpu()).abs().max())
+    bound = TOL[dtype] * (scale if scale is not None else float(ref.abs().max()) + 1e-30)
+    assert err <= bound, f"max abs err {err:.3e} > {bound:.3e}"
+
+
+def rnd(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(DT[dtype]).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding(dtype):
+    from libllm_b200.csrc import ops
+    table = rnd((1000, 200), dtype, 1)
+    ids = torch.tensor([0, 999, 5, 5, 321], dtype=torch.int32, device=DEV)
+    out = torch.empty((5, 200), dtype=torch.float32, device=DEV)
+    ops.embedding(table, ids, out)
+    assert torch.equal(out.cpu(), P.embedding(table.cpu(), ids.tolist()).float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,parts", [(200, 0), (200, 1), (72, 3), (13000, 2)])
+def test_add_rmsnorm(dtype, hidden, parts):
+    from libllm_b200.csrc import ops
+    T = 7
+    resid = rnd((T, hidden), "float32", 2)
+    delta = rnd((parts, T, hidden), dtype, 3) if parts else None
+    w = rnd((hidden,), "float32", 4) * 0.1 + 1
+    out = torch.empty((T, hidden), dtype=DT[dtype], device=DEV)
+    want = resid.double().cpu() + (delta.double().cpu().sum(0) if parts else 0)
+    r2 = resid.clone()
+    ops.add_rmsnorm(r2, delta, w, 1e-5, out)
+    close(r2, want, "float32")
+    close(out, P.rms_norm(want, w.cpu(), 1e-5), dtype)
+    # a subset of rows, residual left alone
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    r3 = resid.clone()
+    out3 = torch.empty((3, hidden), dtype=DT[dtype], device=DEV)
+    ops.add_rmsnorm(r3, delta, w, 1e-5, out3, rows)
+    assert torch.equal(r3, resid)
+    close(out3, P.rms_norm(want[[6, 0, 3]], w.cpu(), 1e-5), dtype)
+    # add only
+    r4 = resid.clone()
+    ops.add_rmsnorm(r4, delta, None, 0.0, None)
+    close(r4, want, "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    from libllm_b200.csrc import ops
+    gu = rnd((9, 2 * 173), dtype, 5, 2.0)
+    gu[0, 0] = -30.0
+    gu[0, 1] = 30.0
+    out = torch.empty((9, 173), dtype=DT[dtype], device=DEV)
+    ops.swiglu(gu, out)
+    close(out, P.swiglu(gu[:, :173].cpu(), gu[:, 173:].cpu()), dtype)
+
+
+@pytest.mark.parametrize("dtype,out_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 7, 3), (513, 2, 513), (70, 130, 1000), (64, 64, 16)])
+def test_gemm_plain(dtype, out_dtype, M, N, K):
+    from libllm_b200.csrc import ops
+    a, w = rnd((M, K), dtype, 6), rnd((N, K), dtype, 7)
+    bias = rnd((N,), "float32", 8)
+    out = torch.empty((M, N), dtype=DT[out_dtype], device=DEV)
+    ops.gemm_plain(a, w, out, bias)
+    ref = P.linear(a.cpu(), w.cpu(), bias.cpu())
+    close(out, ref, out_dtype, scale=float(ref.abs().max()) + math.sqrt(K) * 1e-1)
+
+
+def test_gemm_plain_rows_do_not_depend_on_the_batch():
+    from libllm_b200.csrc import ops
+    a, w = rnd((130, 300), "float32", 9), rnd((77, 300), "float32", 10)
+    full = torch.empty((130, 77), device=DEV)
+    one = torch.empty((1, 77), device=DEV)
+    ops.gemm_plain(a, w, full)
+    ops.gemm_plain(a[97:98], w, one)
+    assert torch.equal(full[97:98], one)
+
+
+def paged_cache(n_seqs, lens, n_kv, d, page, dtype, seed):
+    """Random keys/values per sequence scattered over shuffled pages."""
+    per = [(l + page - 1) // page for l in lens]
+    n_pages = sum(per) + 3
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(per) + 1
+    table = torch.zeros((n_seqs, width), dtype=torch.int32)
+    K = torch.full((n_pages, n_kv, page, d), 1e4).to(DT[dtype])     # unread places are poisoned
+    V = torch.full((n_pages, n_kv, page, d), -1e4).to(DT[dtype])
+    ks, vs = [], []
+    o = 0
+    for s, l in enumerate(lens):
+        k = (torch.randn((l, n_kv, d), generator=g)).to(DT[dtype])
+        v = (torch.randn((l, n_kv, d), generator=g)).to(DT[dtype])
+        ks.append(k)
+        vs.append(v)
+        for lp in range(per[s]):
+            pg = perm[o]
+            o += 1
+            table[s, lp] = pg
+            n = min(page, l - lp * page)
+            K[pg, :, :n] = k[lp * page:lp * page + n].transpose(0, 1)
+            V[pg, :, :n] = v[lp * page:lp * page + n].transpose(0, 1)
+    return K.to(DEV), V.to(DEV), table.to(DEV), ks, vs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv,d,window", [(4, 2, 16, None), (3, 1, 48, None), (8, 8, 128, None),
+                                                     (6, 2, 256, None), (4, 1, 32, 37), (2, 2, 64, 64)])
+def test_attention_generic(dtype, n_heads, n_kv, d, window):
+    from libllm_b200.csrc import ops
+    page = 16
+    lens = [1, 70, 33, 130]
+    q_lens = [1, 70, 5, 1]          # a whole prompt, the end of one, and single tokens
+    K, V, table, ks, vs = paged_cache(4, lens, n_kv, d, page, dtype, 11)
+    T = sum(q_lens)
+    q = rnd((T, n_heads * d), dtype, 12)
+    tok_seq = torch.tensor([s for s, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lens[s] - n + i for s, n in enumerate(q_lens) for i in range(n)], dtype=torch.int32, device=DEV)
+    out = torch.empty((T, n_heads * d), dtype=DT[dtype], device=DEV)
+    scale = 1 / math.sqrt(d)
+    ops.attention_generic(q, out, K, V, tok_seq, tok_pos, table, n_heads, n_kv, d, page, window, scale)
+    o = 0
+    for s, n in enumerate(q_lens):
+        ref = P.attention_scores_softmax_values(q[o:o + n].cpu().view(n, n_heads, d), ks[s], vs[s], window)
+        close(out[o:o + n].view(n, n_heads, d), ref, dtype, scale=1.0)
+        o += n
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """Key 3 of 900 matches the query strongly; its value must dominate the output."""
+    from libllm_b200.csrc import ops
+    n_heads = n_kv = 1
+    d, page, L = 64, 64, 900
+    K, V, table, ks, vs = paged_cache(1, [L], n_kv, d, page, dtype, 13)
+    q = rnd((1, d), dtype, 14)
+    k3 = (q[0].float().cpu() * 3.0).to(DT[dtype])
+    pg = int(table[0, 0])
+    K[pg, 0, 3] = k3.to(DEV)
+    ks[0][3, 0] = k3
+    out = torch.empty((1, d), dtype=DT[dtype], device=DEV)
+    pos = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    ops.attention_generic(q, out, K, V, torch.zeros(1, dtype=torch.int32, device=DEV), pos, table, 1, 1, d, page,
+                          None, 1 / math.sqrt(d))
+    ref = P.attention_scores_softmax_values(q.cpu().view(1, 1, d), ks[0], vs[0])
+    close(out.view(1, 1, d), ref, dtype, scale=1.0)
+    assert float((out.float().cpu()[0] - vs[0][3, 0].float()).abs().max()) < 0.2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 16), (3, 1, 96)])
+def test_rope_and_cache_write(dtype, n_heads, n_kv, d):
+    from libllm_b200.csrc import ops
+    from libllm_b200.parts.rope import rotary_frequencies
+    page, n_pages = 8, 12
+    lens_past, q_lens = [0, 13, 40], [9, 1, 3]
+    T = sum(q_lens)
+    width = (n_heads + 2 * n_kv) * d
+    qkv = rnd((T, width), dtype, 15)
+    qkv0 = qkv.clone()
+    freqs = torch.tensor(rotary_frequencies(d, 10000.0, None), dtype=torch.float64)
+    pos = torch.arange(64, dtype=torch.float64)
+    ang = pos[:, None] * freqs[None]
+    table = torch.cat([ang.cos(), ang.sin()], 1).float().to(DEV)
+    tok_seq = torch.tensor([s for s, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lens_past[s] + i for s, n in enumerate(q_lens) for i in range(n)], dtype=torch.int32, device=DEV)
+    pt = torch.tensor([[3, 7, 0, 0, 0, 0], [1, 2, 0, 0, 0, 0], [4, 5, 6, 8, 9, 10]], dtype=torch.int32, device=DEV)
+    K = torch.zeros((n_pages, n_kv, page, d), dtype=DT[dtype], device=DEV)
+    V = torch.zeros_like(K)
+    ops.rope_cache_write(qkv, n_heads, n_kv, d, table, tok_seq, tok_pos, pt, K, V, page)
+    x = qkv0.cpu().view(T, n_heads + 2 * n_kv, d)
+    positions = tok_pos.cpu().to(torch.float64)
+    qr = P.rope_rotate(x[:, :n_heads], positions, freqs)
+    kr = P.rope_rotate(x[:, n_heads:n_heads + n_kv], positions, freqs)
+    got = qkv.cpu().view(T, n_heads + 2 * n_kv, d)
+    close(got[:, :n_heads], qr, dtype)
+    for t in range(T):
+        s, p = int(tok_seq[t]), int(tok_pos[t])
+        pg = int(pt[s, p // page])
+        close(K[pg, :, p % page], kr[t], dtype)
+        assert torch.equal(V[pg, :, p % page].cpu(), x[t, n_heads + n_kv:])
+    # places no token was written to stay untouched
+    written = {(int(pt[int(tok_seq[t]), int(tok_pos[t]) // page]), int(tok_pos[t]) % page) for t in range(T)}
+    for pg in range(n_pages):
+        for r in range(page):
+            if (pg, r) not in written:
+                assert float(K[pg, :, r].abs().max()) == 0.0
+
+
+def test_argmax_and_ties():
+    from libllm_b200.csrc import ops
+    logits = rnd((5, 3001), "float32", 16)
+    logits[1, 17] = logits[1, 2900] = 50.0          # tie: the lower index wins
+    logits[2, 3000] = 60.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    want = [P.sample_token(logits[i].cpu(), 0.0, 0, 1.0, 0.0) for i in range(5)]
+    assert out.tolist() == want and want[1] == 17 and want[2] == 3000
+
+
+def _interval_ok(logits_row, temperature, top_k, top_p, u, token):
+    """``token`` is what the plain sampler returns for a number within 1e-5 of u."""
+    return any(P.sample_token(logits_row, temperature, top_k, top_p, min(max(u + du, 0.0), 0.9999999)) == token
+               for du in (0.0, -1e-5, 1e-5))
+
+
+@pytest.mark.parametrize("vocab", [331, 128256])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 50, 0.8), (0.7, 5, 1.0), (1.3, 1, 0.5), (0.8, 0, 1.0),
+                                                      (1.0, 1024, 0.95)])
+def test_sampling_matches_plain_sampler(vocab, temperature, top_k, top_p):
+    from libllm_b200.csrc import ops
+    B = 6
+    logits = rnd((B, vocab), "float32", 17, 3.0)
+    logits[0, 5] = logits[0, 9] = logits[0].max() + 1.0        # tied leaders
+    us = [0.0, 0.1234, 0.5, 0.77, 0.999, 0.31]
+    uni = torch.tensor(us, dtype=torch.float32, device=DEV)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temperature, top_k, top_p, uni, out)
+    for i in range(B):
+        assert _interval_ok(logits[i].cpu(), temperature, min(top_k, vocab), top_p, us[i], int(out[i])), (i, int(out[i]))
+    # a row's draw does not depend on its neighbours
+    out1 = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample(logits[3:4], temperature, top_k, top_p, uni[3:4], out1)
+    assert int(out1[0]) == int(out[3])
+    # temperature 0 is argmax
+    ops.sample(logits, 0.0, top_k, top_p, uni, out)
+    assert out.tolist() == logits.argmax(-1).tolist() or int(out[0]) == 5
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from libllm_b200.csrc import ops
+    from libllm_b200.errors import ExtensionError, UnsupportedError
+    with pytest.raises(ExtensionError):
+        ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))          # host tensors: no CPU fallback
+    logits = rnd((1, 100), "float32", 18)
+    with pytest.raises(UnsupportedError):
+        ops.sample(logits, 1.0, 5000, 1.0, torch.zeros(1, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
