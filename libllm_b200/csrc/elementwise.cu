@@ -110,9 +110,10 @@ LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype,
 }
 
 // ---------------------------------------------------------------- swiglu
-// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(a) = a / (1 + exp(-a)).
-template <typename T>
-__global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, int inter, size_t total) {
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(a) = a / (1 + exp(-a)).  TI is the
+// type of the stacked gate|up product (32-bit when the product gives that), T of out.
+template <typename TI, typename T>
+__global__ void swiglu_kernel(const TI *__restrict__ gu, T *__restrict__ out, int inter, size_t total) {
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
@@ -123,7 +124,7 @@ __global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, int
   }
 }
 
-LLM_EXPORT int llm_swiglu(int dtype, const void *gu, void *out, int n_tokens, int inter,
+LLM_EXPORT int llm_swiglu(int in_dtype, int dtype, const void *gu, void *out, int n_tokens, int inter,
                           cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
@@ -131,12 +132,14 @@ LLM_EXPORT int llm_swiglu(int dtype, const void *gu, void *out, int n_tokens, in
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  if (dtype == LLM_F32)
-    swiglu_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>((const float *)gu, (float *)out, inter, total);
-  else if (dtype == LLM_BF16)
-    swiglu_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, inter, total);
+  if (in_dtype == LLM_F32 && dtype == LLM_F32)
+    swiglu_kernel<float, float><<<(unsigned)blocks, threads, 0, stream>>>((const float *)gu, (float *)out, inter, total);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16)
+    swiglu_kernel<float, __nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const float *)gu, (__nv_bfloat16 *)out, inter, total);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16)
+    swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, inter, total);
   else
-    LLM_FAIL("swiglu: unknown dtype %d", dtype);
+    LLM_FAIL("swiglu: unsupported dtypes in %d out %d", in_dtype, dtype);
   LLM_CHECK_LAUNCH("swiglu");
   return LLM_OK;
 }

@@ -109,13 +109,13 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Opti
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(gu[t, i]) * gu[t, I + i]."""
+    """out[t, i] = silu(gu[t, i]) * gu[t, I + i]; gu may be 32-bit while out is bfloat16."""
     _on_gpu(gu, out)
     T, two_i = gu.shape
-    assert gu.is_contiguous() and out.is_contiguous() and out.dtype == gu.dtype
+    assert gu.is_contiguous() and out.is_contiguous()
     assert tuple(out.shape) == (T, two_i // 2)
-    _call("elementwise", "llm_swiglu", [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
-          dtype_code(gu.dtype), _ptr(gu), _ptr(out), T, two_i // 2, _stream())
+    _call("elementwise", "llm_swiglu", [c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(gu.dtype), dtype_code(out.dtype), _ptr(gu), _ptr(out), T, two_i // 2, _stream())
     return out
 
 
@@ -139,26 +139,29 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
 
 
 # ------------------------------------------------------------------ rope + cache write
-def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, table: torch.Tensor,
-                     tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
-                     kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], page_size: int,
-                     write_cache: bool = True) -> None:
-    """Rotates the q and k heads of the stacked rows in place and appends k and v to the
-    paged cache [pages, kv_heads, page_size, d] of one layer."""
-    _on_gpu(qkv, table, tok_seq, tok_pos, page_table, kcache, vcache)
+def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                     table: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
+                     page_table: torch.Tensor, kcache: Optional[torch.Tensor],
+                     vcache: Optional[torch.Tensor], page_size: int, write_cache: bool = True) -> None:
+    """Rotates the q heads of the stacked rows into ``q_out`` and, rotated (k) or as they
+    are (v), appends k and v to the paged cache [pages, kv_heads, page_size, d] of one
+    layer.  ``qkv`` may be 32-bit while ``q_out`` and the cache are bfloat16."""
+    _on_gpu(qkv, q_out, table, tok_seq, tok_pos, page_table, kcache, vcache)
     T = qkv.shape[0]
     assert qkv.stride(1) == 1 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+    assert q_out.stride(1) == 1 and q_out.shape[0] == T and q_out.shape[1] >= n_heads * head_dim
     assert table.dtype == torch.float32 and table.is_contiguous() and table.dim() == 2
     assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
     if write_cache:
-        assert kcache.dtype == qkv.dtype and kcache.is_contiguous() and vcache.is_contiguous()
+        assert kcache.dtype == q_out.dtype and kcache.is_contiguous() and vcache.is_contiguous()
         assert tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     _call("rope", "llm_rope_cache_write",
-          [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
-          dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), T, n_heads, n_kv, head_dim, _ptr(table),
-          table.shape[0], table.shape[1], _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table),
-          page_table.stride(0), _ptr(kcache), _ptr(vcache), page_size, 1 if write_cache else 0, _stream())
+          [c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p,
+           c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(qkv.dtype), dtype_code(q_out.dtype), _ptr(qkv), qkv.stride(0), _ptr(q_out),
+          q_out.stride(0), T, n_heads, n_kv, head_dim, _ptr(table), table.shape[0], table.shape[1],
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache),
+          page_size, 1 if write_cache else 0, _stream())
 
 
 # ------------------------------------------------------------------ attention (generic)

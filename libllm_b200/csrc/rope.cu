@@ -16,30 +16,35 @@
 
 LLM_DEFINE_LAST_ERROR(llm_rope_last_error)
 
-template <typename T>
-__global__ void rope_cache_write_kernel(T *__restrict__ qkv, long long row_stride, int n_heads,
+// TI: type of the stacked q|k|v rows (the product's output, 32-bit when the product can
+// give that, so that q and k are rounded once, after the rotation); T: type of the
+// rotated queries and of the cache.
+template <typename TI, typename T>
+__global__ void rope_cache_write_kernel(const TI *__restrict__ qkv, long long row_stride,
+                                        T *__restrict__ q_out, long long q_stride, int n_heads,
                                         int n_kv, int d, const float *__restrict__ table,
                                         int table_rows, int rot_dim, const int *__restrict__ tok_seq,
                                         const int *__restrict__ tok_pos, const int *__restrict__ page_table,
                                         int pt_stride, T *__restrict__ kcache, T *__restrict__ vcache,
-                                        int page_size, int write_cache) {
+                                        int page_size) {
   const int t = blockIdx.x;
   const int slot = blockIdx.y;                 // 0..n_heads-1: q, then k heads, then v heads
   const int pos = tok_pos[t];
-  T *row = qkv + (size_t)t * row_stride + (size_t)slot * d;
+  const TI *row = qkv + (size_t)t * row_stride + (size_t)slot * d;
   const int half = rot_dim / 2;
   const bool is_v = slot >= n_heads + n_kv;
   const bool is_k = !is_v && slot >= n_heads;
-  T *dst = nullptr;
-  if ((is_k || is_v) && write_cache) {
+  T *dst;
+  if (is_k || is_v) {
     const int kvh = is_k ? slot - n_heads : slot - n_heads - n_kv;
     const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
     T *base = is_k ? kcache : vcache;
     dst = base + (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * d;
+  } else {
+    dst = q_out + (size_t)t * q_stride + (size_t)slot * d;
   }
   if (is_v) {
-    if (dst)
-      for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = row[i];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_float<T>(to_float(row[i]));
     return;
   }
   const int p = pos < table_rows ? pos : table_rows - 1;   // the host refuses longer sequences
@@ -47,21 +52,17 @@ __global__ void rope_cache_write_kernel(T *__restrict__ qkv, long long row_strid
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float c = cs[i], s = cs[half + i];
     const float a = to_float(row[i]), b = to_float(row[i + half]);
-    const T ra = from_float<T>(a * c - b * s);
-    const T rb = from_float<T>(b * c + a * s);
-    if (is_k) {
-      if (dst) { dst[i] = ra; dst[i + half] = rb; }
-      row[i] = ra; row[i + half] = rb;
-    } else {
-      row[i] = ra; row[i + half] = rb;
-    }
+    dst[i] = from_float<T>(a * c - b * s);
+    dst[i + half] = from_float<T>(b * c + a * s);
   }
   // Channels beyond the rotated ones (rot_dim < d) pass through unchanged.
-  if (is_k && dst)
-    for (int i = rot_dim + threadIdx.x; i < d; i += blockDim.x) dst[i] = row[i];
+  for (int i = rot_dim + threadIdx.x; i < d; i += blockDim.x) dst[i] = from_float<T>(to_float(row[i]));
 }
 
-LLM_EXPORT int llm_rope_cache_write(int dtype, void *qkv, long long row_stride, int n_tokens, int n_heads,
+// in_dtype: type of qkv; dtype: type of q_out and of the cache.  With write_cache == 0
+// only the query heads are processed (the layer reads another layer's keys and values).
+LLM_EXPORT int llm_rope_cache_write(int in_dtype, int dtype, const void *qkv, long long row_stride,
+                                    void *q_out, long long q_stride, int n_tokens, int n_heads,
                                     int n_kv, int d, const float *table, int table_rows, int rot_dim,
                                     const int *tok_seq, const int *tok_pos, const int *page_table,
                                     int pt_stride, void *kcache, void *vcache, int page_size,
@@ -70,14 +71,17 @@ LLM_EXPORT int llm_rope_cache_write(int dtype, void *qkv, long long row_stride, 
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0, "rope: bad sizes");
   LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim > 0, "rope: rotated width %d does not fit head size %d", rot_dim, d);
   LLM_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope: too many heads for one launch");
-  dim3 grid(n_tokens, n_heads + 2 * n_kv);
+  dim3 grid(n_tokens, write_cache ? n_heads + 2 * n_kv : n_heads);
   int threads = d / 2 >= 64 ? 64 : 32;
-  if (dtype == LLM_F32)
-    rope_cache_write_kernel<float><<<grid, threads, 0, stream>>>((float *)qkv, row_stride, n_heads, n_kv, d, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride, (float *)kcache, (float *)vcache, page_size, write_cache);
-  else if (dtype == LLM_BF16)
-    rope_cache_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16 *)qkv, row_stride, n_heads, n_kv, d, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride, (__nv_bfloat16 *)kcache, (__nv_bfloat16 *)vcache, page_size, write_cache);
-  else
-    LLM_FAIL("rope: unknown dtype %d", dtype);
+#define ROPE_LAUNCH(TI, T)                                                                              \
+  rope_cache_write_kernel<TI, T><<<grid, threads, 0, stream>>>(                                         \
+      (const TI *)qkv, row_stride, (T *)q_out, q_stride, n_heads, n_kv, d, table, table_rows, rot_dim,  \
+      tok_seq, tok_pos, page_table, pt_stride, (T *)kcache, (T *)vcache, page_size)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) ROPE_LAUNCH(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) ROPE_LAUNCH(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("rope: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef ROPE_LAUNCH
   LLM_CHECK_LAUNCH("rope_cache_write");
   return LLM_OK;
 }

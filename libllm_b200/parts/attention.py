@@ -65,16 +65,18 @@ class Attention(Mixer):
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: Optional[LayerCache],
                 state: Optional[Dict[str, torch.Tensor]]) -> torch.Tensor:
         s = self.spec
-        qkv = linear(x, self.w_qkv, self.b_qkv)
-        if self.position is not None:
-            ops.rope_cache_write(qkv, s.n_heads, s.n_kv_heads, s.head_dim, self.position.table,
-                                 ctx.tok_seq, ctx.tok_pos, cache.page_table, cache.k, cache.v,
-                                 cache.page_size, cache.writes)
-        else:
+        # The products hand over 32-bit results: q and k are rounded to the engine's
+        # type once, after the rotation, and the residual addition gets an unrounded term.
+        qkv = linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+        if self.position is None:
             raise UnsupportedError("attention without a position encoding is not built")
-        out = fast.attention(ctx, qkv, cache, s, self.scale)
+        q = torch.empty((ctx.n_tokens, self.q_width), dtype=ctx.dtype, device=ctx.device)
+        ops.rope_cache_write(qkv, q, s.n_heads, s.n_kv_heads, s.head_dim, self.position.table,
+                             ctx.tok_seq, ctx.tok_pos, cache.page_table, cache.k, cache.v,
+                             cache.page_size, cache.writes)
+        out = fast.attention(ctx, q, cache, s, self.scale)
         if out is None:
-            out = torch.empty((ctx.n_tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
-            ops.attention_generic(qkv, out, cache.k, cache.v, ctx.tok_seq, ctx.tok_pos, cache.page_table,
+            out = torch.empty((ctx.n_tokens, self.q_width), dtype=ctx.dtype, device=ctx.device)
+            ops.attention_generic(q, out, cache.k, cache.v, ctx.tok_seq, ctx.tok_pos, cache.page_table,
                                   s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size, s.window, self.scale)
-        return linear(out, self.w_o, out_dtype=torch.float32 if ctx.dtype == torch.float32 else None)
+        return linear(out, self.w_o, out_dtype=torch.float32)

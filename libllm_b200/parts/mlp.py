@@ -32,7 +32,7 @@ class SwiGLU(FeedForward):
         return ["elementwise", "gemm_plain"]
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
-        gu = linear(x, self.w_gate_up)
-        m = torch.empty((x.shape[0], self.spec.intermediate), dtype=gu.dtype, device=gu.device)
+        gu = linear(x, self.w_gate_up, out_dtype=torch.float32)
+        m = torch.empty((x.shape[0], self.spec.intermediate), dtype=ctx.dtype, device=ctx.device)
         ops.swiglu(gu, m)
-        return linear(m, self.w_down)
+        return linear(m, self.w_down, out_dtype=torch.float32)

@@ -86,21 +86,46 @@ def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
     return float((got.to(torch.float64).cpu() - ref).abs().max() / ref.abs().mean())
 
 
-# Bounds on rel_err.  float32: the engine and the plain implementation (float64) differ by
-# 32-bit rounding alone.  bfloat16: the reference's bound for its half-precision path
-# (src/libllm/llama_test.cc:49).
-TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+def rms_err(got: torch.Tensor, ref: torch.Tensor) -> float:
+    """||got - ref|| / ||ref||: unlike the maximum it is not set by one rare rounding."""
+    ref = ref.to(torch.float64)
+    d = got.to(torch.float64).cpu() - ref
+    return float((d * d).mean().sqrt() / (ref * ref).mean().sqrt())
+
+
+# Bounds: (on rel_err, on rms_err).
+# float32: the engine and the plain implementation (float64) differ by 32-bit rounding alone.
+# bfloat16: a bfloat16 matrix product takes bfloat16 inputs, so activations are rounded
+#   (8 significant bits) at five places per layer and before the output matrix.  The plain
+#   implementation itself, with these roundings and nothing else changed
+#   (``forward_logits(..., act_dtype=torch.bfloat16)``), stands 1.0e-2 to 2.1e-2 (rel_err)
+#   and 2e-3 to 4e-3 (rms_err) from its exact form on the tiny models here, and a
+#   perturbation of 1e-7 before the roundings moves it by as much again, because
+#   roundings flip and the flips spread: tests/test_plain.py measures both.  The bounds
+#   are twice that floor.  (The reference allows 2e-2 in rel_err for float16, whose
+#   rounding is eight times finer: src/libllm/llama_test.cc:49.)
+TOL = {"float32": (2e-5, 2e-6), "bfloat16": (4e-2, 8e-3)}
 
 
 def check_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "") -> None:
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: logits are not finite"
+    tol_max, tol_rms = TOL[dtype]
     e = rel_err(got, ref)
-    assert e < TOL[dtype], f"{what}: rel err {e:.3e} exceeds {TOL[dtype]:.1e} ({dtype})"
+    assert e < tol_max, f"{what}: rel err {e:.3e} exceeds {tol_max:.1e} ({dtype})"
+    r = rms_err(got, ref)
+    assert r < tol_rms, f"{what}: rms err {r:.3e} exceeds {tol_rms:.1e} ({dtype})"
     # argmax agrees wherever the plain implementation's top-2 margin is above the tolerance
     ref64 = ref.to(torch.float64)
-    top2 = ref64.topk(2, dim=-1).values
-    margin = top2[..., 0] - top2[..., 1]
-    clear = margin > 2 * TOL[dtype] * float(ref64.abs().mean())
-    same = got.cpu().argmax(-1) == ref64.argmax(-1)
-    assert bool((same | ~clear).all()), f"{what}: argmax differs where the margin is clear"
+    if ref64.shape[-1] >= 2:
+        top2 = ref64.topk(2, dim=-1).values
+        margin = top2[..., 0] - top2[..., 1]
+        clear = margin > 2 * tol_max * float(ref64.abs().mean())
+        same = got.cpu().argmax(-1) == ref64.argmax(-1)
+        assert bool((same | ~clear).all()), f"{what}: argmax differs where the margin is clear"
+
+
+def check_against_plain(got: torch.Tensor, c: dict, w, toks, dtype: str, what: str = "") -> None:
+    """The engine's logits for one whole request against the plain implementation."""
+    import plain_llama as P
+    check_logits(got, P.forward_logits(c, w, toks), dtype, what)

@@ -26,6 +26,17 @@ import torch
 DT = torch.float64
 
 
+def stored(x: torch.Tensor, act_dtype) -> torch.Tensor:
+    """``x`` as it reads back after being stored in ``act_dtype`` (None: kept exact).
+
+    A bfloat16 engine has to round an activation wherever a bfloat16 matrix product or the
+    cache takes it: the outputs of the norms, q/k (after the rotation) and v, the attention
+    output and the SwiGLU output.  With ``act_dtype=torch.bfloat16`` the plain
+    implementation rounds at exactly these places and nowhere else, which gives the tests
+    a reference that differs from a bfloat16 engine by accumulation order only."""
+    return x if act_dtype is None else x.to(act_dtype).to(DT)
+
+
 # ----------------------------------------------------------------------------- config
 def read_config(folder: str) -> dict:
     """config.json as a plain dict with the defaults the reference's loader applies:
@@ -147,7 +158,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -
 
 
 def attention_block(x, positions, w: Dict[str, torch.Tensor], prefix: str, c: dict,
-                    window: Optional[int] = None) -> torch.Tensor:
+                    window: Optional[int] = None, act_dtype=None) -> torch.Tensor:
     """q, k, v projections, rotation of q and k, attention, output projection
     (src/libllm/llama.cc:178-225).  The reference multiplies by one stacked matrix
     [Wq; Wk; Wv] and slices (src/libllm/llama.cc:180-186, tools/llama_exporter.py:64-71);
@@ -158,9 +169,10 @@ def attention_block(x, positions, w: Dict[str, torch.Tensor], prefix: str, c: di
     k = linear(x, w[prefix + "k_proj.weight"], w.get(prefix + "k_proj.bias")).view(T, nKV, d)
     v = linear(x, w[prefix + "v_proj.weight"], w.get(prefix + "v_proj.bias")).view(T, nKV, d)
     freqs = rope_frequencies(d, c["rope_theta"], c["rope_scaling"])
-    q = rope_rotate(q, positions, freqs)
-    k = rope_rotate(k, positions, freqs)
-    o = attention_scores_softmax_values(q, k, v, window)
+    q = stored(rope_rotate(q, positions, freqs), act_dtype)
+    k = stored(rope_rotate(k, positions, freqs), act_dtype)
+    v = stored(v, act_dtype)
+    o = stored(attention_scores_softmax_values(q, k, v, window), act_dtype)
     return linear(o.reshape(T, nH * d), w[prefix + "o_proj.weight"])
 
 
@@ -171,24 +183,25 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate * (1.0 / (1.0 + torch.exp(-gate))) * up.to(DT)
 
 
-def feed_forward(x, w: Dict[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def feed_forward(x, w: Dict[str, torch.Tensor], prefix: str, act_dtype=None) -> torch.Tensor:
     """down(swiglu(gate(x), up(x))), no biases (src/libllm/llama.cc:81-98)."""
     g = linear(x, w[prefix + "gate_proj.weight"])
     u = linear(x, w[prefix + "up_proj.weight"])
-    return linear(swiglu(g, u), w[prefix + "down_proj.weight"])
+    return linear(stored(swiglu(g, u), act_dtype), w[prefix + "down_proj.weight"])
 
 
-def decoder_layer(x, positions, w, i: int, c: dict) -> torch.Tensor:
+def decoder_layer(x, positions, w, i: int, c: dict, act_dtype=None) -> torch.Tensor:
     """Pre-norm residual block: x + attn(norm(x)), then h + mlp(norm(h))
     (src/libllm/llama.cc:251-267)."""
     p = f"model.layers.{i}."
     eps = c["rms_norm_eps"]
-    h = x + attention_block(rms_norm(x, w[p + "input_layernorm.weight"], eps), positions, w,
-                            p + "self_attn.", c)
-    return h + feed_forward(rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp.")
+    h = x + attention_block(stored(rms_norm(x, w[p + "input_layernorm.weight"], eps), act_dtype), positions,
+                            w, p + "self_attn.", c, None, act_dtype)
+    return h + feed_forward(stored(rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), act_dtype), w,
+                            p + "mlp.", act_dtype)
 
 
-def forward_logits(c: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> torch.Tensor:
+def forward_logits(c: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], act_dtype=None) -> torch.Tensor:
     """Logits at every position of one whole sequence, [T, vocab], float64: embedding,
     the layers in order, the last norm (src/libllm/llama.cc:294-303), then the output
     matrix (src/libllm/llama.cc:305-308), which is the embedding table when
@@ -197,8 +210,8 @@ def forward_logits(c: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> t
     x = embedding(w["model.embed_tokens.weight"], ids)
     positions = torch.arange(len(ids))
     for i in range(c["num_hidden_layers"]):
-        x = decoder_layer(x, positions, w, i, c)
-    x = rms_norm(x, w["model.norm.weight"], c["rms_norm_eps"])
+        x = decoder_layer(x, positions, w, i, c, act_dtype)
+    x = stored(rms_norm(x, w["model.norm.weight"], c["rms_norm_eps"]), act_dtype)
     head = w["model.embed_tokens.weight"] if c["tie_word_embeddings"] else w["lm_head.weight"]
     return linear(x, head)
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_llama as P
-from helpers import TINY, check_logits, model_folder, plain_weights, tokens_for
+from helpers import TINY, check_against_plain, check_logits, model_folder, plain_weights, tokens_for
 from replay import replay_batch
 
 pytestmark = pytest.mark.gpu
@@ -36,7 +36,7 @@ def test_each_request_alone_and_whole(name, dtype):
     for i, n in enumerate([1, 2, 5, 33, 64, 65, 131]):
         toks = tokens_for(name, n, i)
         got = replay_batch(engine, [("r", toks, n)])["r"]
-        check_logits(got, plain(c, w, toks), dtype, f"{name} whole len {n}")
+        check_against_plain(got, c, w, toks, dtype, f"{name} whole len {n}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -46,7 +46,7 @@ def test_last_32_tokens_one_by_one(name, dtype):
     for i, n in enumerate([33, 100, 160]):
         toks = tokens_for(name, n, 10 + i)
         got = replay_batch(engine, [("r", toks, n - 32)])["r"]
-        check_logits(got, plain(c, w, toks), dtype, f"{name} last-32 len {n}")
+        check_against_plain(got, c, w, toks, dtype, f"{name} last-32 len {n}")
 
 
 WORKLOADS = {
@@ -72,7 +72,7 @@ def test_unequal_batches_one_after_another(name, dtype):
             reqs.append((f"b{b}r{j}", tokens_for(name, total, 100 * b + j), p))
         got = replay_batch(engine, reqs)
         for rid, toks, _ in reqs:
-            check_logits(got[rid], plain(c, w, toks), dtype, f"{name} batch {b} {rid}")
+            check_against_plain(got[rid], c, w, toks, dtype, f"{name} batch {b} {rid}")
     assert engine.cache.groups[0].pool.in_use == 0
 
 
@@ -82,7 +82,7 @@ def test_long_decoding(dtype):
     engine, c, w = setup("B", dtype)
     toks = tokens_for("B", 300, 77)
     got = replay_batch(engine, [("r", toks, 1)])["r"]
-    check_logits(got, plain(c, w, toks), dtype, "long decoding")
+    check_against_plain(got, c, w, toks, dtype, "long decoding")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -93,10 +93,9 @@ def test_first_tokens_of_a_sequence(dtype):
     long_ = tokens_for("A", 90, 6)
     alone = replay_batch(engine, [("s", short, 1)])["s"]
     both = replay_batch(engine, [("l", long_, 60), ("s", short, 1)])
-    ref = plain(c, w, short)
-    check_logits(alone, ref, dtype, "first tokens alone")
-    check_logits(both["s"], ref, dtype, "first tokens beside a long request")
-    check_logits(both["l"], plain(c, w, long_), dtype, "long neighbour")
+    check_against_plain(alone, c, w, short, dtype, "first tokens alone")
+    check_against_plain(both["s"], c, w, short, dtype, "first tokens beside a long request")
+    check_against_plain(both["l"], c, w, long_, dtype, "long neighbour")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -106,7 +105,7 @@ def test_prompt_cut_into_chunks(dtype):
     reqs = [("a", tokens_for("C", 100, 1), 100), ("b", tokens_for("C", 30, 2), 30)]
     got = replay_batch(engine, reqs)
     for rid, toks, _ in reqs:
-        check_logits(got[rid], plain(c, w, toks), dtype, f"chunked {rid}")
+        check_against_plain(got[rid], c, w, toks, dtype, f"chunked {rid}")
 
 
 def test_batch_composition_does_not_change_float32_results():

@@ -61,10 +61,10 @@ def test_add_rmsnorm(dtype, hidden, parts):
     close(r4, want, "float32")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_swiglu(dtype):
+@pytest.mark.parametrize("dtype,in_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
+def test_swiglu(dtype, in_dtype):
     from libllm_b200.csrc import ops
-    gu = rnd((9, 2 * 173), dtype, 5, 2.0)
+    gu = rnd((9, 2 * 173), in_dtype, 5, 2.0)
     gu[0, 0] = -30.0
     gu[0, 1] = 30.0
     out = torch.empty((9, 173), dtype=DT[dtype], device=DEV)
@@ -165,17 +165,18 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
     assert float((out.float().cpu()[0] - vs[0][3, 0].float()).abs().max()) < 0.2
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype,in_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
 @pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 16), (3, 1, 96)])
-def test_rope_and_cache_write(dtype, n_heads, n_kv, d):
+def test_rope_and_cache_write(dtype, in_dtype, n_heads, n_kv, d):
     from libllm_b200.csrc import ops
     from libllm_b200.parts.rope import rotary_frequencies
     page, n_pages = 8, 12
     lens_past, q_lens = [0, 13, 40], [9, 1, 3]
     T = sum(q_lens)
     width = (n_heads + 2 * n_kv) * d
-    qkv = rnd((T, width), dtype, 15)
+    qkv = rnd((T, width), in_dtype, 15)
     qkv0 = qkv.clone()
+    q_out = torch.zeros((T, n_heads * d), dtype=DT[dtype], device=DEV)
     freqs = torch.tensor(rotary_frequencies(d, 10000.0, None), dtype=torch.float64)
     pos = torch.arange(64, dtype=torch.float64)
     ang = pos[:, None] * freqs[None]
@@ -185,18 +186,18 @@ def test_rope_and_cache_write(dtype, n_heads, n_kv, d):
     pt = torch.tensor([[3, 7, 0, 0, 0, 0], [1, 2, 0, 0, 0, 0], [4, 5, 6, 8, 9, 10]], dtype=torch.int32, device=DEV)
     K = torch.zeros((n_pages, n_kv, page, d), dtype=DT[dtype], device=DEV)
     V = torch.zeros_like(K)
-    ops.rope_cache_write(qkv, n_heads, n_kv, d, table, tok_seq, tok_pos, pt, K, V, page)
+    ops.rope_cache_write(qkv, q_out, n_heads, n_kv, d, table, tok_seq, tok_pos, pt, K, V, page)
+    assert torch.equal(qkv, qkv0)
     x = qkv0.cpu().view(T, n_heads + 2 * n_kv, d)
     positions = tok_pos.cpu().to(torch.float64)
     qr = P.rope_rotate(x[:, :n_heads], positions, freqs)
     kr = P.rope_rotate(x[:, n_heads:n_heads + n_kv], positions, freqs)
-    got = qkv.cpu().view(T, n_heads + 2 * n_kv, d)
-    close(got[:, :n_heads], qr, dtype)
+    close(q_out.cpu().view(T, n_heads, d), qr, dtype)
     for t in range(T):
         s, p = int(tok_seq[t]), int(tok_pos[t])
         pg = int(pt[s, p // page])
         close(K[pg, :, p % page], kr[t], dtype)
-        assert torch.equal(V[pg, :, p % page].cpu(), x[t, n_heads + n_kv:])
+        assert torch.equal(V[pg, :, p % page].cpu(), x[t, n_heads + n_kv:].to(DT[dtype]))
     # places no token was written to stay untouched
     written = {(int(pt[int(tok_seq[t]), int(tok_pos[t]) // page]), int(tok_pos[t]) % page) for t in range(T)}
     for pg in range(n_pages):
