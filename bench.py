@@ -1,0 +1,282 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one GPU, as one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of Llama-3.2-1B with random bfloat16 weights, a batch of 8
+sequences with 2,048-token prompts in a 4,096-token context; a "step" is one decode
+step of the whole batch.  ``value`` is decoded tokens a second with the step timed on the
+device (CUDA events around K graph replays); ``e2e`` is the same through the Python entry
+point (``Model.generate``), host token ids in and sampled ids out at every step.  The line
+also carries the prefill of 2,048 tokens, the decode step's bytes against the memory
+bandwidth, and decode at batch 1 and 64.  The decode step reads about 3 GB (weights and
+cache), far more than the 126 MB L2, so no flush is needed between steps.
+Only one GPU is supported: for --gpus N > 1 it says so and exits with 2."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_1B = dict(model_type="llama", num_hidden_layers=16, hidden_size=2048, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=128256,
+                rope_theta=500000.0,
+                rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192),
+                rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072,
+                hidden_act="silu")
+CONTEXT = 4096
+PROMPT = 2048
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+def model_numbers(c):
+    """Bytes a decode step has to read per weight pass and per cached token; prefill flops."""
+    H, L, I, V = c["hidden_size"], c["num_hidden_layers"], c["intermediate_size"], c["vocab_size"]
+    nH, nKV, d = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    per_layer = H * (nH + 2 * nKV) * d + nH * d * H + 3 * H * I + 2 * H
+    weight_bytes = 2 * (L * per_layer + V * H + H)          # every weight used once, the output matrix included
+    kv_bytes_per_token = 2 * L * nKV * d * 2
+
+    def prefill_flops(T, rows=1):
+        lin = 2 * T * L * (H * (nH + 2 * nKV) * d + nH * d * H + 3 * H * I)
+        att = L * 4 * nH * d * T * (T + 1) // 2            # q k^T and p v over the causal half
+        return lin + att + 2 * rows * V * H
+    return weight_bytes, kv_bytes_per_token, prefill_flops
+
+
+def decode_rate(model, batch, steps, warmup, vocab, seed=0):
+    """Decoded tokens a second at ``batch`` with the step timed on the device."""
+    import torch
+    from libllm_b200.engine import GREEDY, StepItem
+    eng = model.engine
+    g = torch.Generator().manual_seed(seed)
+    slots = [eng.open_sequence() for _ in range(batch)]
+    try:
+        prompts = torch.randint(0, vocab, (batch, PROMPT), generator=g).tolist()
+        # prompts in one step (the engine cuts it into launches of max_step_tokens)
+        _, toks = eng.step([StepItem(s, p, [PROMPT - 1]) for s, p in zip(slots, prompts)], GREEDY,
+                           return_logits=False)
+        cur = toks.cpu().tolist()
+        for _ in range(warmup):
+            _, toks = eng.step([StepItem(s, [t], [0]) for s, t in zip(slots, cur)], GREEDY, return_logits=False)
+            cur = toks.cpu().tolist()
+        # the graph that the timed steps replay, and its launch count
+        key = [k for k in eng._graphs if k[0] == batch][-1]
+        graph = eng._graphs[key]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            # device-only timing: the same step replayed (tokens and positions as uploaded last)
+            graph.graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end) / steps
+        ctx_len = eng.sequence_length(slots[0])
+        return batch * 1000.0 / ms, ms, ctx_len, graph
+    finally:
+        for s in slots:
+            eng.close_sequence(s)
+
+
+def count_graph_launches(model, batch):
+    """Kernel launches of this library in one decode step of ``batch`` (counted while the
+    step runs outside a graph)."""
+    import torch
+    from libllm_b200.csrc import ops
+    from libllm_b200.engine import GREEDY, StepItem
+    eng = model.engine
+    slots = [eng.open_sequence() for _ in range(batch)]
+    try:
+        eng.step([StepItem(s, [1, 2, 3], []) for s in slots])
+        was = eng.use_graphs
+        eng.use_graphs = False
+        n0 = ops.LAUNCHES[0]
+        eng.step([StepItem(s, [5], [0]) for s in slots], GREEDY, return_logits=False)
+        n = ops.LAUNCHES[0] - n0
+        eng.use_graphs = was
+        torch.cuda.synchronize()
+        return n
+    finally:
+        for s in slots:
+            eng.close_sequence(s)
+
+
+def e2e_rate(model, batch, steps, warmup, vocab, seed=1):
+    """Decoded tokens a second through Model.generate: every step copies the step's token
+    ids and tables from pinned host memory to the device and reads the sampled ids back."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    prompts = torch.randint(0, vocab, (batch, PROMPT), generator=g).tolist()
+    stamps = []
+
+    def on_token(i, tok):
+        if i == 0:
+            torch.cuda.synchronize()
+            stamps.append(time.perf_counter())
+
+    from libllm_b200.engine import SamplingParams, generate
+    generate(model.engine, prompts, warmup + steps + 1, SamplingParams(0.0, 1, 1.0), seed=0, stop_tokens=[],
+             max_batch=batch, on_token=on_token)
+    # stamps[0] follows the prompt step; steps warmup+1 .. warmup+steps are timed
+    t = stamps[warmup + steps] - stamps[warmup]
+    graph = [v for k, v in model.engine._graphs.items() if k[0] == batch][-1]
+    h2d = graph.desc.host.numel() * 4
+    return batch * steps / t, h2d, batch * 4
+
+
+def prefill_rate(model, vocab, flops_fn, peak_tflops, reps=3):
+    import torch
+    from libllm_b200.engine import StepItem
+    eng = model.engine
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, vocab, (PROMPT,), generator=g).tolist()
+    times = []
+    for r in range(reps + 2):
+        s = eng.open_sequence()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepItem(s, prompt, [PROMPT - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        eng.close_sequence(s)
+        if r >= 2:
+            times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    flops = flops_fn(PROMPT)
+    return dict(value=PROMPT * 1000.0 / ms, tokens=PROMPT, ms=ms, frac=flops / (ms * 1e-3) / (peak_tflops * 1e12))
+
+
+def run_reference(args):
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "ling0322/libllm has no Python package to install offline (python/ holds a stale ctypes "
+                      "wrapper with no build; the C++ library needs a downloaded libunwind and a .llmpkg model "
+                      "exported from a checkpoint): nothing under baseline/_ref" if not os.path.isdir(ref_dir)
+                      else "baseline/_ref exists but holds no runnable benchmark of the reference"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from libllm_b200 import Model
+    cfg = dict(LLAMA_1B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+    vocab = cfg["vocab_size"]
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT, max_seq_len=CONTEXT)
+
+    launches_per_step = count_graph_launches(model, args.batch)
+    sampler = ClockSampler()
+    sampler.start()
+    rate, ms, ctx_len, _ = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+    clocks = sampler.stop()
+    e2e, h2d, d2h = e2e_rate(model, args.batch, args.steps, args.warmup, vocab)
+    prefill = prefill_rate(model, vocab, flops_fn, pk["bf16_tflops"])
+    step_bytes = wbytes + args.batch * ctx_len * kv_per_tok
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            r, _, _, _ = decode_rate(model, b, max(8, args.steps // 2), args.warmup, vocab)
+            points[f"decode_b{b}"] = round(r, 1)
+    line = {
+        "metric": "decode tok/s (Llama-3.2-1B layer sizes, batch 8, 2048-token prompts, 4096 context)",
+        "value": round(rate, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "llama-3.2-1b-sizes", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "context_at_timing": ctx_len,
+                   "parallelism": "single-gpu", "weights": "random bf16 N(0,0.02), tied",
+                   "l2": "step reads more than L2 (no flush)", "peaks": pk["source"]},
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "prefill": {k: (round(v, 4) if isinstance(v, float) else v) for k, v in prefill.items()},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

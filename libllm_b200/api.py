@@ -43,11 +43,34 @@ class Model:
                  use_graphs: bool = True, max_step_tokens: int = 8192):
         if device == Device.CPU:
             raise InvalidArgError("this library has no CPU path: device must be CUDA or AUTO")
-        self.weights = _Weights.from_folder(path, dtype=dtype, device=f"cuda:{cuda_device}",
-                                            max_positions=max_seq_len)
-        self.engine = Engine(self.weights, max_tokens=max_tokens, max_seq_len=max_seq_len,
-                             use_graphs=use_graphs, max_step_tokens=max_step_tokens)
+        weights = _Weights.from_folder(path, dtype=dtype, device=f"cuda:{cuda_device}",
+                                       max_positions=max_seq_len)
+        self._attach(weights, max_tokens, max_seq_len, use_graphs, max_step_tokens)
         self.path = path
+
+    def _attach(self, weights, max_tokens, max_seq_len, use_graphs, max_step_tokens) -> None:
+        self.weights = weights
+        self.engine = Engine(weights, max_tokens=max_tokens, max_seq_len=max_seq_len,
+                             use_graphs=use_graphs, max_step_tokens=max_step_tokens)
+        self.path = None
+
+    @classmethod
+    def from_random(cls, config_json: dict, seed: int = 0, dtype: str = "bfloat16", max_tokens: int = 65536,
+                    max_seq_len: Optional[int] = None, cuda_device: int = 0, use_graphs: bool = True,
+                    max_step_tokens: int = 8192) -> "Model":
+        """The random-weights mode without a folder: tensors are drawn on the device
+        (matrices N(0, 0.02), norm weights 1 + U(-0.1, 0.1)) from ``seed``."""
+        import torch
+        from .config import architecture_for
+        from .weights.random_model import random_tensors
+        device = f"cuda:{cuda_device}"
+        config = architecture_for(config_json["model_type"]).parse(config_json)
+        tensors = random_tensors(config_json, seed, torch.bfloat16, device)
+        self = cls.__new__(cls)
+        self._attach(_Weights.from_tensors(config, tensors, dtype=dtype, device=device,
+                                           max_positions=max_seq_len),
+                     max_tokens, max_seq_len, use_graphs, max_step_tokens)
+        return self
 
     @property
     def name(self) -> str:

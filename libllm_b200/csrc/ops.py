@@ -40,6 +40,7 @@ def _on_gpu(*tensors) -> None:
 
 
 _protos = {}
+LAUNCHES = [0]        # kernel launches issued through this module (graph replays not included)
 
 
 def _fn(family: str, name: str, argtypes):
@@ -58,6 +59,7 @@ def _fn(family: str, name: str, argtypes):
 
 def _call(family: str, name: str, argtypes, *args) -> None:
     f, err = _fn(family, name, argtypes)
+    LAUNCHES[0] += 1
     status = f(*args)
     if status != 0:
         msg = err().decode("utf-8", "replace")

@@ -258,7 +258,7 @@ class Engine:
                             uni.append(uniforms[int(want_base[p.index]) + j])
                 o += p.count
             widths = [self._table_width(pieces)] * len(self.cache.groups)
-            desc = _Descriptor(self.device, T, len(pieces), len(want_rows), widths)
+            desc = self._eager_descriptor(T, len(pieces), len(want_rows), widths)
             self._fill(desc, pieces, items, want_rows, uni if uniforms is not None else None)
             max_kv = max(p.past + p.start + p.count for p in pieces)
             ctx, tables = self._context(desc, pieces, len(want_rows), all(p.count == 1 for p in pieces), max_kv)
@@ -287,6 +287,16 @@ class Engine:
         if perm is not None:
             tokens = tokens[perm]
         return (logits if return_logits else None), tokens
+
+    def _eager_descriptor(self, T: int, B: int, W: int, widths: List[int]) -> _Descriptor:
+        """Staging buffers are kept per shape: pinned allocations are slow to make."""
+        key = (T, B, W, tuple(widths))
+        desc = self._eager_desc.get(key)
+        if desc is None:
+            if len(self._eager_desc) >= 64:
+                self._eager_desc.pop(next(iter(self._eager_desc)))
+            desc = self._eager_desc[key] = _Descriptor(self.device, T, B, W, widths)
+        return desc
 
     def _table_width(self, pieces: List[_Piece]) -> int:
         need = max((p.past + p.start + p.count + self.page_size - 1) // self.page_size for p in pieces)
