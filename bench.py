@@ -220,6 +220,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print a short line (for profiling; not a bench record)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -237,9 +239,17 @@ def main():
     pk = peaks()
     wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
     vocab = cfg["vocab_size"]
-    max_batch = max(args.batch, 1 if args.no_points else 64)
+    max_batch = max(args.batch, 1 if (args.no_points or args.only) else 64)
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT, max_seq_len=CONTEXT)
 
+    if args.only == "decode":
+        rate, ms, ctx_len, _ = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+        print(json.dumps({"only": "decode", "batch": args.batch, "tok_s": round(rate, 1), "ms_per_step": round(ms, 4),
+                          "context": ctx_len}))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", **prefill_rate(model, vocab, flops_fn, pk["bf16_tflops"])}))
+        return 0
     launches_per_step = count_graph_launches(model, args.batch)
     sampler = ClockSampler()
     sampler.start()

@@ -1,0 +1,264 @@
+// Attention for decoding steps: every sequence brings one query token, keys and values
+// come from the paged bfloat16 cache.  Split over the keys (flash-decoding): CTA
+// (split, kv head, sequence) reduces `chunk` keys for all query heads of its group with a
+// running maximum and sum, then a second kernel joins the splits in split order.
+//
+// The kernel is bound by reading K and V once (4 flop per byte with 4 query heads per kv
+// head), so it is written for loads: D/8 lanes share a key, each lane fetching 16 bytes of
+// K and of V for its 8 channels, four keys per lane group in flight, consecutive lane
+// groups on consecutive keys so that a CTA reads 2 KB runs of a page.  Scores, softmax and
+// the weighted sum are 32-bit; exp is taken as exp2 of pre-scaled scores.
+//
+// Reference counterpart: FlashAttention-2's split-KV forward and its combine kernel as the
+// reference calls them for one query token (src/flint/cuda/flash_attn.cc:165-180); head h
+// reads kv head h / (heads / kv_heads), scores are scaled by 1/sqrt(d), and one query sees
+// every cached key (src/flint/operators.cc:43-56, 115-124).
+#include "common.cuh"
+#include <math.h>
+
+LLM_DEFINE_LAST_ERROR(llm_attention_decode_last_error)
+
+constexpr int AD_THREADS = 128;
+constexpr int AD_KB = 4;              // keys per lane group per iteration
+
+__device__ __forceinline__ void unpack8(const uint4 &raw, float (&f)[8]) {
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
+                        const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
+                        const int *__restrict__ tok_pos, const int *__restrict__ page_table, int pt_stride,
+                        int n_kv, int page_size, int chunk, int window, float scale_log2,
+                        float *__restrict__ ws_o, float *__restrict__ ws_ml, int n_splits,
+                        __nv_bfloat16 *__restrict__ out, long long out_stride) {
+  constexpr int LPK = D / 8;                 // lanes per key
+  constexpr int GPW = 32 / LPK;              // lane groups per warp
+  constexpr int GROUPS = (AD_THREADS / 32) * GPW;
+  __shared__ float sm_o[AD_THREADS / 32][G][D];
+  __shared__ float sm_m[AD_THREADS / 32][G], sm_l[AD_THREADS / 32][G];
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int len = tok_pos[b] + 1;
+  const int kstart = window > 0 ? max(0, len - window) : 0;
+  const int c0 = split * chunk;
+  const int c1 = min(c0 + chunk, len);
+  if (c0 >= len || c1 <= kstart) return;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPK, grp = warp * GPW + lane / LPK;
+  const int n_heads = n_kv * G;
+
+  float qr[G][8];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(q + (size_t)b * q_stride + (size_t)(kvh * G + h) * D + sub * 8);
+    unpack8(raw, qr[h]);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) qr[h][c] *= scale_log2;
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[h][c] = 0.f;
+  }
+  const int *pt = page_table + (size_t)b * pt_stride;
+
+  for (int base = c0; base < c1; base += GROUPS * AD_KB) {
+    uint4 kraw[AD_KB], vraw[AD_KB];
+    bool ok[AD_KB];
+#pragma unroll
+    for (int u = 0; u < AD_KB; ++u) {
+      const int key = base + u * GROUPS + grp;
+      ok[u] = key < c1 && key >= kstart;
+      const int kk = ok[u] ? key : c1 - 1;                    // a key that exists; its weight is zero
+      const int page = pt[kk / page_size];
+      const size_t off = (((size_t)page * n_kv + kvh) * page_size + (kk % page_size)) * D + sub * 8;
+      kraw[u] = *reinterpret_cast<const uint4 *>(kc + off);
+      vraw[u] = *reinterpret_cast<const uint4 *>(vc + off);
+    }
+    float s[AD_KB][G];
+#pragma unroll
+    for (int u = 0; u < AD_KB; ++u) {
+      float kf[8];
+      unpack8(kraw[u], kf);
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        float d = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) d = fmaf(qr[h][c], kf[c], d);
+        s[u][h] = d;
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1)
+#pragma unroll
+      for (int u = 0; u < AD_KB; ++u)
+#pragma unroll
+        for (int h = 0; h < G; ++h) s[u][h] += __shfl_xor_sync(0xffffffffu, s[u][h], o);
+    float vf[AD_KB][8];
+#pragma unroll
+    for (int u = 0; u < AD_KB; ++u) unpack8(vraw[u], vf[u]);
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < AD_KB; ++u) mx = fmaxf(mx, ok[u] ? s[u][h] : -INFINITY);
+      const float m_new = fmaxf(m[h], mx);
+      if (m_new == -INFINITY) continue;                       // this group has seen no key yet
+      const float alpha = exp2f(m[h] - m_new);                // 0 when m was -inf
+      l[h] *= alpha;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[h][c] *= alpha;
+#pragma unroll
+      for (int u = 0; u < AD_KB; ++u) {
+        const float p = ok[u] ? exp2f(s[u][h] - m_new) : 0.f;
+        l[h] += p;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[h][c] = fmaf(p, vf[u][c], acc[h][c]);
+      }
+      m[h] = m_new;
+    }
+  }
+
+  // Join the lane groups of a warp (fixed order: partner at distance LPK, 2 LPK, ...).
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+      const float m_new = fmaxf(m[h], mo);
+      const float sa = m[h] == -INFINITY ? 0.f : exp2f(m[h] - m_new);
+      const float sb = mo == -INFINITY ? 0.f : exp2f(mo - m_new);
+      l[h] = l[h] * sa + lo * sb;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[h][c], o);
+        acc[h][c] = acc[h][c] * sa + ao * sb;
+      }
+      m[h] = m_new;
+    }
+  }
+  if (lane < LPK) {
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) sm_o[warp][h][sub * 8 + c] = acc[h][c];
+      if (sub == 0) {
+        sm_m[warp][h] = m[h];
+        sm_l[warp][h] = l[h];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += AD_THREADS) {
+    const int h = idx / D, c = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AD_THREADS / 32; ++w) M = fmaxf(M, sm_m[w][h]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < AD_THREADS / 32; ++w) {
+      const float f = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - M);
+      L += sm_l[w][h] * f;
+      O += sm_o[w][h][c] * f;
+    }
+    const int head = kvh * G + h;
+    if (n_splits == 1) {
+      out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L);
+    } else {
+      const size_t slot = ((size_t)b * n_heads + head) * n_splits + split;
+      ws_o[slot * D + c] = O;
+      if (c == 0) {
+        ws_ml[slot * 2] = M;
+        ws_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Joins the splits of one (sequence, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+__global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, const float *__restrict__ ws_ml,
+                                                const int *__restrict__ tok_pos, int n_heads, int D, int chunk,
+                                                int window, int n_splits, __nv_bfloat16 *__restrict__ out,
+                                                long long out_stride) {
+  const int head = blockIdx.x, b = blockIdx.y;
+  const int len = tok_pos[b] + 1;
+  const int kstart = window > 0 ? max(0, len - window) : 0;
+  const int first = kstart / chunk, last = (len - 1) / chunk;
+  const size_t slot0 = ((size_t)b * n_heads + head) * n_splits;
+  float M = -INFINITY;
+  for (int s = first; s <= last; ++s) M = fmaxf(M, ws_ml[(slot0 + s) * 2]);
+  float L = 0.f;
+  for (int s = first; s <= last; ++s) L += ws_ml[(slot0 + s) * 2 + 1] * exp2f(ws_ml[(slot0 + s) * 2] - M);
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float O = 0.f;
+    for (int s = first; s <= last; ++s) O += ws_o[(slot0 + s) * D + c] * exp2f(ws_ml[(slot0 + s) * 2] - M);
+    out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L);
+  }
+}
+
+template <int D, int G>
+static int launch_decode(const void *q, long long q_stride, const void *kc, const void *vc, const int *tok_pos,
+                         const int *page_table, int pt_stride, int n_seqs, int n_kv, int page_size, int chunk,
+                         int n_splits, int window, float scale, float *ws_o, float *ws_ml, void *out,
+                         long long out_stride, cudaStream_t stream) {
+  dim3 grid(n_splits, n_kv, n_seqs);
+  attention_decode_kernel<D, G><<<grid, AD_THREADS, 0, stream>>>(
+      (const __nv_bfloat16 *)q, q_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, tok_pos, page_table,
+      pt_stride, n_kv, page_size, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
+      (__nv_bfloat16 *)out, out_stride);
+  LLM_CHECK_LAUNCH("attention_decode");
+  if (n_splits > 1) {
+    dim3 cgrid(n_kv * G, n_seqs);
+    attention_decode_combine_kernel<<<cgrid, D < 64 ? 32 : 64, 0, stream>>>(ws_o, ws_ml, tok_pos, n_kv * G, D, chunk,
+                                                                          window, n_splits, (__nv_bfloat16 *)out,
+                                                                          out_stride);
+    LLM_CHECK_LAUNCH("attention_decode_combine");
+  }
+  return LLM_OK;
+}
+
+// 1 if the (head size, group size) pair has an instantiation, else 0.
+LLM_EXPORT int llm_attention_decode_supports(int d, int group) {
+  const bool d_ok = d == 16 || d == 32 || d == 64 || d == 128;
+  const bool g_ok = group == 1 || group == 2 || group == 3 || group == 4 || group == 8;
+  return d_ok && g_ok;
+}
+
+// q [B, heads*d] bfloat16 (rotated), caches [pages, kv_heads, page_size, d], tok_pos[b] =
+// position of sequence b's query (it sees keys 0..tok_pos[b]).  ws_o needs
+// B*heads*n_splits*d floats and ws_ml B*heads*n_splits*2 when n_splits > 1.
+LLM_EXPORT int llm_attention_decode(const void *q, long long q_stride, void *out, long long out_stride,
+                                    const void *kc, const void *vc, const int *tok_pos, const int *page_table,
+                                    int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
+                                    int chunk, int n_splits, int window, float scale, float *ws_o, float *ws_ml,
+                                    cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv > 0 && n_kv <= 65535 && n_heads % n_kv == 0, "attention_decode: bad sizes");
+  const int group = n_heads / n_kv;
+  LLM_REQUIRE(llm_attention_decode_supports(d, group), "attention_decode: head size %d with %d query heads per kv head is not built", d, group);
+  LLM_REQUIRE(chunk > 0 && chunk % 16 == 0 && n_splits >= 1, "attention_decode: chunk %d must be a positive multiple of 16", chunk);
+  LLM_REQUIRE(n_splits == 1 || (ws_o && ws_ml), "attention_decode: splits need scratch memory");
+  LLM_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
+#define AD_CASE(DD, GG)                                                                                         \
+  if (d == DD && group == GG)                                                                                   \
+    return launch_decode<DD, GG>(q, q_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_kv, page_size, \
+                                 chunk, n_splits, window, scale, ws_o, ws_ml, out, out_stride, stream);
+#define AD_CASES(DD) AD_CASE(DD, 1) AD_CASE(DD, 2) AD_CASE(DD, 3) AD_CASE(DD, 4) AD_CASE(DD, 8)
+  AD_CASES(16) AD_CASES(32) AD_CASES(64) AD_CASES(128)
+#undef AD_CASES
+#undef AD_CASE
+  LLM_FAIL("attention_decode: no kernel for head size %d, group %d", d, group);
+}

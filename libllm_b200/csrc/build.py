@@ -36,6 +36,8 @@ FAMILIES: Dict[str, dict] = {
     "rope": dict(sources=["rope.cu"], headers=["common.cuh"]),
     "attention_generic": dict(sources=["attention_generic.cu"], headers=["common.cuh"]),
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
+    "gemv": dict(sources=["gemv.cu"], headers=["common.cuh"]),
+    "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh"]),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -204,3 +204,57 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, u
           _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], float(temperature), int(top_k),
           float(top_p), _ptr(uniforms), _ptr(out), _stream())
     return out
+
+
+# ------------------------------------------------------------------ small-batch product (bfloat16)
+GEMV_MAX_TOKENS = 64
+
+
+def gemv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= GEMV_MAX_TOKENS
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64; with ``swiglu`` w is the stacked
+    gate|up matrix [2I, K] and out[M, I] = silu(gate) * up."""
+    _on_gpu(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.stride(1) == 1 and tuple(out.shape) == (M, N // 2 if swiglu else N)
+    _call("gemv", "llm_gemv_bf16",
+          [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
+          _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(0) if M > 1 else out.shape[1],
+          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, _stream())
+    return out
+
+
+# ------------------------------------------------------------------ attention for decoding (bfloat16)
+def attention_decode_supported(head_dim: int, group: int) -> bool:
+    lib = build.load("attention_decode")
+    f = lib.llm_attention_decode_supports
+    f.argtypes, f.restype = [c_int, c_int], c_int
+    return bool(f(head_dim, group))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                     tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                     page_size: int, chunk: int, n_splits: int, window: Optional[int], scale: float,
+                     ws_o: Optional[torch.Tensor], ws_ml: Optional[torch.Tensor]) -> torch.Tensor:
+    """One query token per sequence over the paged cache, keys split into ``n_splits``
+    runs of ``chunk``; ``ws_o``/``ws_ml`` are the scratch the splits are joined through."""
+    _on_gpu(q, out, kcache, vcache, tok_pos, page_table, ws_o, ws_ml)
+    B = q.shape[0]
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and tok_pos.numel() >= B
+    if n_splits > 1:
+        assert ws_o.dtype == torch.float32 and ws_o.numel() >= B * n_heads * n_splits * head_dim
+        assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
+    _call("attention_decode", "llm_attention_decode",
+          [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
+          _ptr(q), q.stride(0) if B > 1 else q.shape[1], _ptr(out), out.stride(0) if B > 1 else out.shape[1],
+          _ptr(kcache), _ptr(vcache), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), B, n_heads, n_kv,
+          head_dim, page_size, chunk, n_splits, int(window or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _stream())
+    return out

@@ -86,7 +86,7 @@ class Model:
         return self
 
     def kernel_families(self) -> List[str]:
-        fams = {"elementwise", "gemm_plain", "sampling"}
+        fams = {"elementwise", "gemm_plain", "sampling", "gemv"}
         for layer in self.layers:
             fams.update(layer.kernel_families())
         return sorted(fams)

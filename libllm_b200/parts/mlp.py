@@ -7,6 +7,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.state_map import TensorNeed
+from . import fast
 from .base import FeedForward, StepContext
 from .linear import linear
 from .registry import part
@@ -29,9 +30,12 @@ class SwiGLU(FeedForward):
         self.w_down = fetch(needs[2])
 
     def kernel_families(self) -> List[str]:
-        return ["elementwise", "gemm_plain"]
+        return ["elementwise", "gemm_plain", "gemv"]
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
+        m = fast.small_batch_linear(x, self.w_gate_up, ctx.dtype, swiglu=True) if x.dtype == torch.bfloat16 else None
+        if m is not None:
+            return linear(m, self.w_down, out_dtype=torch.float32)
         gu = linear(x, self.w_gate_up, out_dtype=torch.float32)
         m = torch.empty((x.shape[0], self.spec.intermediate), dtype=ctx.dtype, device=ctx.device)
         ops.swiglu(gu, m)

@@ -254,3 +254,57 @@ def test_kernels_refuse_what_they_cannot_do():
     logits = rnd((1, 100), "float32", 18)
     with pytest.raises(UnsupportedError):
         ops.sample(logits, 1.0, 5000, 1.0, torch.zeros(1, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 200, 80), (3, 331, 176), (16, 2048, 2048), (33, 130, 520),
+                                   (64, 1000, 4096), (7, 17, 8)])
+def test_small_batch_product(out_dtype, M, N, K):
+    from libllm_b200.csrc import ops
+    x, w = rnd((M, K), "bfloat16", 20), rnd((N, K), "bfloat16", 21, 0.05)
+    out = torch.empty((M, N), dtype=DT[out_dtype], device=DEV)
+    ops.gemv_bf16(x, w, out)
+    ref = P.linear(x.cpu(), w.cpu())
+    close(out, ref, out_dtype, scale=float(ref.abs().max()))
+    # one token's result does not depend on the others in the batch: bit for bit when the
+    # batch has the same size, to rounding when the size (and with it the K split) differs
+    x2 = rnd((M, K), "bfloat16", 99)
+    x2[M - 1] = x[M - 1]
+    out2 = torch.empty((M, N), dtype=DT[out_dtype], device=DEV)
+    ops.gemv_bf16(x2, w, out2)
+    assert torch.equal(out2[M - 1], out[M - 1])
+    one = torch.empty((1, N), dtype=DT[out_dtype], device=DEV)
+    ops.gemv_bf16(x[M - 1:M], w, one)
+    close(one, ref[M - 1:M], out_dtype, scale=float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 96, 64), (5, 173, 80), (8, 8192, 2048), (40, 300, 256)])
+def test_small_batch_product_with_swiglu(M, I, K):
+    from libllm_b200.csrc import ops
+    x, w = rnd((M, K), "bfloat16", 22), rnd((2 * I, K), "bfloat16", 23, 0.2)
+    out = torch.empty((M, I), dtype=torch.bfloat16, device=DEV)
+    ops.gemv_bf16(x, w, out, swiglu=True)
+    gu = P.linear(x.cpu(), w.cpu())
+    close(out, P.swiglu(gu[:, :I], gu[:, I:]), "bfloat16")
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d,window", [(4, 2, 16, None), (3, 1, 32, None), (32, 8, 64, None),
+                                                     (8, 1, 128, None), (8, 8, 64, None), (6, 2, 128, 100)])
+@pytest.mark.parametrize("chunk,n_splits", [(64, 16), (192, 6), (1024, 1)])
+def test_attention_decode(n_heads, n_kv, d, window, chunk, n_splits):
+    from libllm_b200.csrc import ops
+    page = 64
+    lens = [1, 70, 333, 1000, 64]
+    B = len(lens)
+    K, V, table, ks, vs = paged_cache(B, lens, n_kv, d, page, "bfloat16", 24)
+    q = rnd((B, n_heads * d), "bfloat16", 25)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    out = torch.empty((B, n_heads * d), dtype=torch.bfloat16, device=DEV)
+    ws_o = torch.full((B * n_heads * n_splits * d,), float("nan"), device=DEV)
+    ws_ml = torch.full((B * n_heads * n_splits * 2,), float("nan"), device=DEV)
+    assert ops.attention_decode_supported(d, n_heads // n_kv)
+    ops.attention_decode(q, out, K, V, pos, table, n_heads, n_kv, d, page, chunk, n_splits, window, 1 / math.sqrt(d),
+                         ws_o, ws_ml)
+    for b in range(B):
+        ref = P.attention_scores_softmax_values(q[b:b + 1].cpu().view(1, n_heads, d), ks[b], vs[b], window)
+        close(out[b].view(1, n_heads, d), ref, "bfloat16", scale=1.0)
