@@ -72,20 +72,33 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
 #pragma unroll
     for (int c = 0; c < 8; ++c) acc[h][c] = 0.f;
   }
-  const int *pt = page_table + (size_t)b * pt_stride;
+  // The chunk's page numbers, once, so that no load address waits on another load.
+  extern __shared__ int s_pages[];
+  {
+    const int *pt = page_table + (size_t)b * pt_stride + c0 / page_size;
+    const int n_pg = (c1 - c0 + page_size - 1) / page_size;
+    for (int i = threadIdx.x; i < n_pg; i += AD_THREADS) s_pages[i] = pt[i];
+  }
+  __syncthreads();
 
-  for (int base = c0; base < c1; base += GROUPS * AD_KB) {
-    uint4 kraw[AD_KB], vraw[AD_KB];
+  constexpr int STEP = GROUPS * AD_KB;
+  auto load = [&](int base, uint4 (&kr)[AD_KB], uint4 (&vr)[AD_KB]) {
+#pragma unroll
+    for (int u = 0; u < AD_KB; ++u) {
+      const int key = base + u * GROUPS + grp;
+      const int kk = key < c1 ? key : c1 - 1;                 // a key that exists; its weight is zero
+      const int page = s_pages[(kk - c0) / page_size];
+      const size_t off = (((size_t)page * n_kv + kvh) * page_size + (kk % page_size)) * D + sub * 8;
+      kr[u] = *reinterpret_cast<const uint4 *>(kc + off);
+      vr[u] = *reinterpret_cast<const uint4 *>(vc + off);
+    }
+  };
+  auto consume = [&](int base, const uint4 (&kraw)[AD_KB], const uint4 (&vraw)[AD_KB]) {
     bool ok[AD_KB];
 #pragma unroll
     for (int u = 0; u < AD_KB; ++u) {
       const int key = base + u * GROUPS + grp;
       ok[u] = key < c1 && key >= kstart;
-      const int kk = ok[u] ? key : c1 - 1;                    // a key that exists; its weight is zero
-      const int page = pt[kk / page_size];
-      const size_t off = (((size_t)page * n_kv + kvh) * page_size + (kk % page_size)) * D + sub * 8;
-      kraw[u] = *reinterpret_cast<const uint4 *>(kc + off);
-      vraw[u] = *reinterpret_cast<const uint4 *>(vc + off);
     }
     float s[AD_KB][G];
 #pragma unroll
@@ -129,6 +142,18 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
       }
       m[h] = m_new;
     }
+  };
+
+  // Two register buffers: the loads of the next round are issued before this round's math.
+  uint4 ka[AD_KB], va[AD_KB], kb[AD_KB], vb[AD_KB];
+  load(c0, ka, va);
+  for (int base = c0; base < c1; base += 2 * STEP) {
+    const bool more = base + STEP < c1;
+    if (more) load(base + STEP, kb, vb);
+    consume(base, ka, va);
+    if (!more) break;
+    if (base + 2 * STEP < c1) load(base + 2 * STEP, ka, va);
+    consume(base + STEP, kb, vb);
   }
 
   // Join the lane groups of a warp (fixed order: partner at distance LPK, 2 LPK, ...).
@@ -215,7 +240,9 @@ static int launch_decode(const void *q, long long q_stride, const void *kc, cons
                          int n_splits, int window, float scale, float *ws_o, float *ws_ml, void *out,
                          long long out_stride, cudaStream_t stream) {
   dim3 grid(n_splits, n_kv, n_seqs);
-  attention_decode_kernel<D, G><<<grid, AD_THREADS, 0, stream>>>(
+  const size_t smem = (size_t)((chunk + page_size - 1) / page_size) * sizeof(int);
+  LLM_REQUIRE(smem <= 16 * 1024, "attention_decode: a chunk of %d keys spans too many pages", chunk);
+  attention_decode_kernel<D, G><<<grid, AD_THREADS, smem, stream>>>(
       (const __nv_bfloat16 *)q, q_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, tok_pos, page_table,
       pt_stride, n_kv, page_size, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
       (__nv_bfloat16 *)out, out_stride);
@@ -249,7 +276,7 @@ LLM_EXPORT int llm_attention_decode(const void *q, long long q_stride, void *out
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv > 0 && n_kv <= 65535 && n_heads % n_kv == 0, "attention_decode: bad sizes");
   const int group = n_heads / n_kv;
   LLM_REQUIRE(llm_attention_decode_supports(d, group), "attention_decode: head size %d with %d query heads per kv head is not built", d, group);
-  LLM_REQUIRE(chunk > 0 && chunk % 16 == 0 && n_splits >= 1, "attention_decode: chunk %d must be a positive multiple of 16", chunk);
+  LLM_REQUIRE(chunk > 0 && chunk % page_size == 0 && n_splits >= 1, "attention_decode: chunk %d must be a positive multiple of the page size", chunk);
   LLM_REQUIRE(n_splits == 1 || (ws_o && ws_ml), "attention_decode: splits need scratch memory");
   LLM_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
 #define AD_CASE(DD, GG)                                                                                         \

@@ -44,7 +44,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 template <int NT, int MT, int UNROLL, bool SWIGLU, typename TO>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloat16 *__restrict__ W,
-            TO *__restrict__ out, long long ldo, int M, int N, int K, int k_split) {
+            TO *__restrict__ out, long long ldo, int M, int N, int K, int k_split, int kb_per_part,
+            long long part_stride) {
   constexpr int SETS = SWIGLU ? 2 : 1;
   extern __shared__ float red[];          // [k_split][row_groups][SETS*MT*NT*4][32]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -85,8 +86,11 @@ gemv_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloa
     xrow[n] = x + (size_t)(xok[n] ? tok : 0) * ldx;
   }
 
-  const int n_kblocks = (K + 31) / 32;
-  for (int kb0 = ks * UNROLL; kb0 < n_kblocks; kb0 += k_split * UNROLL) {
+  // blockIdx.y selects a part of K; each part writes its own partial result.
+  const int kb_first = blockIdx.y * kb_per_part;
+  const int n_kblocks = min((K + 31) / 32, kb_first + kb_per_part);
+  out += (size_t)blockIdx.y * part_stride;
+  for (int kb0 = kb_first + ks * UNROLL; kb0 < n_kblocks; kb0 += k_split * UNROLL) {
     uint4 a[UNROLL][SETS][MT][2];
     uint4 b[UNROLL][NT];
 #pragma unroll
@@ -177,14 +181,19 @@ gemv_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloa
 
 template <int NT, int MT, int UNROLL, bool SWIGLU, typename TO>
 static int launch_gemv(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N,
-                       int K, cudaStream_t stream) {
+                       int K, int k_parts, long long part_stride, cudaStream_t stream) {
   constexpr int SETS = SWIGLU ? 2 : 1;
   const int n_out = SWIGLU ? N / 2 : N;
-  const int n_kblocks = (K + 31) / 32;
-  // Split K over as many warps as keeps about 8 blocks of 32 per warp; the other warps
-  // of the CTA take further rows.
+  const int kb_per_part = ((K + 31) / 32 + k_parts - 1) / k_parts;
+  const int n_kblocks = kb_per_part;
+  // Split K over the warps of a CTA while each warp keeps at least two rounds of loads;
+  // when the matrix has too few rows to give every SM two CTAs, split further (down to
+  // one round per warp), since CTAs, not warps, are what spreads over the SMs.
   int k_split = 1;
-  while (k_split < GEMV_WARPS && n_kblocks / (k_split * 2) >= 8 * UNROLL / 2) k_split *= 2;
+  while (k_split < GEMV_WARPS && n_kblocks / (k_split * 2) >= 4 * UNROLL) k_split *= 2;
+  while (k_split < GEMV_WARPS && n_kblocks / (k_split * 2) >= UNROLL &&
+         (n_out + (GEMV_WARPS / k_split) * 16 * MT - 1) / ((GEMV_WARPS / k_split) * 16 * MT) < 2 * 148)
+    k_split *= 2;
   const int row_groups = GEMV_WARPS / k_split;
   const int rows_per_cta = row_groups * 16 * MT;
   const int grid = (n_out + rows_per_cta - 1) / rows_per_cta;
@@ -192,36 +201,53 @@ static int launch_gemv(const void *x, long long ldx, const void *W, void *out, l
   auto kern = gemv_kernel<NT, MT, UNROLL, SWIGLU, TO>;
   if (smem > 48 * 1024)
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv attribute");
-  kern<<<grid, GEMV_WARPS * 32, smem, stream>>>((const __nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)W, (TO *)out,
-                                                ldo, M, N, K, k_split);
+  kern<<<dim3(grid, k_parts), GEMV_WARPS * 32, smem, stream>>>((const __nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)W,
+                                                               (TO *)out, ldo, M, N, K, k_split, kb_per_part,
+                                                               part_stride);
   LLM_CHECK_LAUNCH("gemv");
   return LLM_OK;
 }
 
 template <bool SWIGLU, typename TO>
 static int dispatch_gemv(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N,
-                         int K, cudaStream_t stream) {
-  if (M <= 8) return launch_gemv<1, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, stream);
-  if (M <= 16) return launch_gemv<2, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, stream);
-  if (M <= 32) return launch_gemv<4, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, stream);
-  return launch_gemv<8, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, stream);
+                         int K, int k_parts, long long part_stride, cudaStream_t stream) {
+  if (M <= 8) return launch_gemv<1, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+  if (M <= 16) return launch_gemv<2, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+  if (M <= 32) return launch_gemv<4, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+  return launch_gemv<8, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+}
+
+// How many parts of K a product of this shape is best cut into so that the GPU has
+// about two CTAs per SM; 1 when the matrix has rows enough.  The caller adds the parts.
+LLM_EXPORT int llm_gemv_suggest_parts(int M, int N, int K) {
+  const int unroll = M <= 16 ? 4 : 2;
+  const int ctas = (N + 15) / 16;
+  const int kblocks = (K + 31) / 32;
+  int parts = 1;
+  while (parts < 8 && ctas * parts < 2 * 148 && kblocks / (parts * 2) >= GEMV_WARPS * unroll) parts *= 2;
+  return parts;
 }
 
 // x [M, K] bfloat16 (row stride ldx), W [N, K] bfloat16 contiguous, out [M, N] (or
 // [M, N/2] with swiglu) of out_dtype.  M <= 64, K a multiple of 8.
+// With k_parts > 1 (plain product, 32-bit out only) part p covers its share of K and
+// writes to out + p * part_stride; the sum over parts is the product.
 LLM_EXPORT int llm_gemv_bf16(const void *x, long long ldx, const void *W, void *out, long long ldo, int out_dtype,
-                             int M, int N, int K, int swiglu, cudaStream_t stream) {
+                             int M, int N, int K, int swiglu, int k_parts, long long part_stride,
+                             cudaStream_t stream) {
   if (M == 0) return LLM_OK;
   LLM_REQUIRE(M > 0 && M <= 64, "gemv: %d tokens (1..64 are taken)", M);
   LLM_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0, "gemv: K=%d and the row stride must be multiples of 8", K);
   LLM_REQUIRE(!swiglu || N % 2 == 0, "gemv: a stacked gate|up matrix has an even number of rows");
+  LLM_REQUIRE(k_parts >= 1 && k_parts <= 64 && (k_parts == 1 || (!swiglu && out_dtype == LLM_F32)),
+              "gemv: parts of K need a plain product with 32-bit output");
   LLM_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemv: operands must be 16-byte aligned");
   if (swiglu) {
-    if (out_dtype == LLM_BF16) return dispatch_gemv<true, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, stream);
-    if (out_dtype == LLM_F32) return dispatch_gemv<true, float>(x, ldx, W, out, ldo, M, N, K, stream);
+    if (out_dtype == LLM_BF16) return dispatch_gemv<true, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+    if (out_dtype == LLM_F32) return dispatch_gemv<true, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
   } else {
-    if (out_dtype == LLM_BF16) return dispatch_gemv<false, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, stream);
-    if (out_dtype == LLM_F32) return dispatch_gemv<false, float>(x, ldx, W, out, ldo, M, N, K, stream);
+    if (out_dtype == LLM_BF16) return dispatch_gemv<false, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+    if (out_dtype == LLM_F32) return dispatch_gemv<false, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
   }
   LLM_FAIL("gemv: unknown output dtype %d", out_dtype);
 }

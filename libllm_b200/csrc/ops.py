@@ -216,17 +216,30 @@ def gemv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def gemv_suggest_parts(M: int, N: int, K: int) -> int:
+    lib = build.load("gemv")
+    f = lib.llm_gemv_suggest_parts
+    f.argtypes, f.restype = [c_int, c_int, c_int], c_int
+    return int(f(M, N, K))
+
+
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64; with ``swiglu`` w is the stacked
-    gate|up matrix [2I, K] and out[M, I] = silu(gate) * up."""
+    gate|up matrix [2I, K] and out[M, I] = silu(gate) * up.  A 3-d ``out`` [parts, M, N]
+    (32-bit) receives partial products over parts of K, to be added by the caller."""
     _on_gpu(x, w, out)
     M, K = x.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.stride(1) == 1 and tuple(out.shape) == (M, N // 2 if swiglu else N)
+    parts, stride = 1, 0
+    if out.dim() == 3:
+        parts, stride = out.shape[0], out.stride(0)
+        assert out.dtype == torch.float32 and not swiglu and out.is_contiguous()
+    assert w.shape[1] == K and out.stride(-1) == 1 and tuple(out.shape[-2:]) == (M, N // 2 if swiglu else N)
     _call("gemv", "llm_gemv_bf16",
-          [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
-          _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(0) if M > 1 else out.shape[1],
-          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, _stream())
+          [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
+           c_longlong, c_void_p],
+          _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(-2) if M > 1 else out.shape[-1],
+          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _stream())
     return out
 
 

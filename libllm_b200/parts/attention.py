@@ -79,4 +79,4 @@ class Attention(Mixer):
             out = torch.empty((ctx.n_tokens, self.q_width), dtype=ctx.dtype, device=ctx.device)
             ops.attention_generic(q, out, cache.k, cache.v, ctx.tok_seq, ctx.tok_pos, cache.page_table,
                                   s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size, s.window, self.scale)
-        return linear(out, self.w_o, out_dtype=torch.float32)
+        return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)

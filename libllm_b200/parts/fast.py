@@ -18,22 +18,29 @@ ENABLED = {
 SM_COUNT = 148
 
 
-def small_batch_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
-                       swiglu: bool = False) -> Optional[torch.Tensor]:
-    """The weight-streaming product for steps of up to 64 tokens."""
+def small_batch_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
+                       parts_ok: bool = False) -> Optional[torch.Tensor]:
+    """The weight-streaming product for steps of up to 64 tokens.  With ``parts_ok`` the
+    result may come as [parts, T, N] partial products over K (32-bit) that the caller adds:
+    matrices with few rows are cut along K so that every SM has work."""
     if not ENABLED["gemv"] or not ops.gemv_supported(x, w):
         return None
     n = w.shape[0] // 2 if swiglu else w.shape[0]
+    if parts_ok and not swiglu and out_dtype == torch.float32:
+        parts = ops.gemv_suggest_parts(x.shape[0], n, x.shape[1])
+        if parts > 1:
+            out = torch.empty((parts, x.shape[0], n), dtype=out_dtype, device=x.device)
+            return ops.gemv_bf16(x, w, out)
     out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
     return ops.gemv_bf16(x, w, out, swiglu)
 
 
 def decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int) -> Tuple[int, int]:
-    """(chunk, n_splits) for decode attention: enough CTAs to fill the GPU about four
-    times over, runs of at least two pages, the same for every step of a captured graph
+    """(chunk, n_splits) for decode attention: enough CTAs to fill the GPU about eight
+    times over at the longest length, runs of at least two pages, the same for every step of a captured graph
     (it depends on the graph's bound on the length, not on the lengths themselves)."""
     pairs = max(1, n_seqs * n_kv)
-    want = max(1, (4 * SM_COUNT + pairs - 1) // pairs)
+    want = max(1, (8 * SM_COUNT + pairs - 1) // pairs)
     most = max(1, max_kv_len // (2 * page_size))
     n_splits = max(1, min(want, most))
     chunk = (max_kv_len + n_splits - 1) // n_splits

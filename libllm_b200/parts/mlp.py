@@ -35,8 +35,8 @@ class SwiGLU(FeedForward):
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
         m = fast.small_batch_linear(x, self.w_gate_up, ctx.dtype, swiglu=True) if x.dtype == torch.bfloat16 else None
         if m is not None:
-            return linear(m, self.w_down, out_dtype=torch.float32)
+            return linear(m, self.w_down, out_dtype=torch.float32, parts_ok=True)
         gu = linear(x, self.w_gate_up, out_dtype=torch.float32)
         m = torch.empty((x.shape[0], self.spec.intermediate), dtype=ctx.dtype, device=ctx.device)
         ops.swiglu(gu, m)
-        return linear(m, self.w_down, out_dtype=torch.float32)
+        return linear(m, self.w_down, out_dtype=torch.float32, parts_ok=True)
