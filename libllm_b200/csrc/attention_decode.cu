@@ -86,7 +86,10 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
 #pragma unroll
     for (int u = 0; u < AD_KB; ++u) {
       const int key = base + u * GROUPS + grp;
-      const int kk = key < c1 ? key : c1 - 1;                 // a key that exists; its weight is zero
+      // A key that exists and lies inside the window (its weight is zero): pages before
+      // the window may have been given back, and their table entries are not page numbers.
+      int kk = key < c1 ? key : c1 - 1;
+      kk = kk < kstart ? kstart : kk;
       const int page = s_pages[(kk - c0) / page_size];
       const size_t off = (((size_t)page * n_kv + kvh) * page_size + (kk % page_size)) * D + sub * 8;
       kr[u] = *reinterpret_cast<const uint4 *>(kc + off);

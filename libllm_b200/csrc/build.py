@@ -134,6 +134,14 @@ def _compile(name: str) -> str:
             pass
         raise ExtensionError(f"nvcc failed for {name} (exit {proc.returncode}):\n{text}")
     os.replace(tmp, out)
+    # Libraries of this family built from earlier versions of the sources are of no use any more.
+    prefix = f"libllm_{name}-"
+    for f in os.listdir(os.path.dirname(out)):
+        if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), f))
+            except OSError:
+                pass
     _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
     return out
 

@@ -70,11 +70,97 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ resid, const TD *__restri
   for (int c = threadIdx.x; c < hidden; c += THREADS) o[c] = from_float<TO>(row_buf[c] * weight[c] * inv);
 }
 
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16 *p) {
+  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16 *p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned *>(&a);
+  raw.y = *reinterpret_cast<unsigned *>(&b);
+  *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+// The same for rows whose width is a multiple of 4 and at most 4 * VPT * THREADS, with up
+// to MAXP parts: every thread issues all its loads (the row, every part, the weight) before
+// it uses one, so the kernel waits for memory once and not once per part.  The values,
+// the order of the additions and the order of the sum of squares within a thread differ
+// from the general kernel's only in which thread owns which columns; like it, a row's
+// result does not depend on the other rows of the launch.
+template <typename TD, typename TO, int THREADS, int VPT, int MAXP>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_vec_kernel(float *__restrict__ resid, const TD *__restrict__ delta, int n_parts,
+                       size_t part_stride, const float *__restrict__ weight, float eps,
+                       TO *__restrict__ out, const int *__restrict__ rows, int hidden) {
+  __shared__ float scratch[THREADS / 32 + 1];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float *x = resid + (size_t)r * hidden;
+  const int n4 = hidden / 4;
+  float4 v[VPT], w[VPT], d[VPT][MAXP];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+      v[j] = ld4(x + 4 * c4);
+      if (out) w[j] = ld4(weight + 4 * c4);
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < n_parts) d[j][p] = ld4(delta + p * part_stride + (size_t)r * hidden + 4 * c4);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < n_parts) {
+          v[j].x += d[j][p].x;
+          v[j].y += d[j][p].y;
+          v[j].z += d[j][p].z;
+          v[j].w += d[j][p].w;
+        }
+      if (!rows && n_parts > 0) st4(x + 4 * c4, v[j]);
+      ss += v[j].x * v[j].x;
+      ss += v[j].y * v[j].y;
+      ss += v[j].z * v[j].z;
+      ss += v[j].w * v[j].w;
+    }
+  }
+  if (!out) return;
+  const float total = block_sum<THREADS>(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  TO *o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4)
+      st4(o + 4 * c4, make_float4(v[j].x * w[j].x * inv, v[j].y * w[j].y * inv, v[j].z * w[j].z * inv,
+                                  v[j].w * w[j].w * inv));
+  }
+}
+
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size_t part_stride,
                               const float *weight, float eps, void *out, const int *rows, int n_rows,
                               int hidden, cudaStream_t stream) {
   constexpr int THREADS = 256;
+  constexpr int VPT = 4, MAXP = 4;
+  const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
+                       (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
+  if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= MAXP) {
+    add_rmsnorm_vec_kernel<TD, TO, THREADS, VPT, MAXP><<<n_rows, THREADS, 0, stream>>>(
+        resid, (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden);
+    LLM_CHECK_LAUNCH("add_rmsnorm");
+    return LLM_OK;
+  }
   size_t smem = (size_t)hidden * sizeof(float);
   auto kern = add_rmsnorm_kernel<TD, TO, THREADS>;
   if (smem > 48 * 1024) {

@@ -356,16 +356,20 @@ class _DecodeGraph:
 
     def run(self) -> None:
         if self.graph is None:
-            # First use: run once outside capture (loads kernels, sizes library
-            # workspaces), then capture the same launches.  Both read the descriptor the
-            # caller has just uploaded, so the cache ends up with the same contents.
+            # First use: the step runs once outside capture (which also loads kernels and
+            # sizes library workspaces) and its results are this call's results; then the
+            # same launches are captured, which executes nothing.  The step must not run
+            # twice: a mixer with state of its own would advance twice.
             side = torch.cuda.Stream(device=self.engine.device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self._body()
+                logits, tokens = self._body()
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
-                self.logits, self.tokens = self._body()
+                self._static = self._body()
+            self.logits, self.tokens = logits, tokens
+            return
         self.graph.replay()
+        self.logits, self.tokens = self._static
