@@ -161,7 +161,7 @@ def bench_attention_prefill(args, timer):
     seq_start = (torch.arange(B + 1, device="cuda", dtype=torch.int32) * T).contiguous()
     seq_past = torch.zeros(B, device="cuda", dtype=torch.int32)
     scale = 1.0 / math.sqrt(d)
-    use_fast = not args.generic and hasattr(ops, "attention_prefill") and ops.attention_prefill_supported(d, nH // nKV)
+    use_fast = not args.generic and ops.attention_prefill_supported(d, 64)
 
     def fn():
         if use_fast:

@@ -38,6 +38,7 @@ FAMILIES: Dict[str, dict] = {
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
     "gemv": dict(sources=["gemv.cu"], headers=["common.cuh"]),
     "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh"]),
+    "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh"]),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

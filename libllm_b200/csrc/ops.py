@@ -271,3 +271,34 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
           _ptr(kcache), _ptr(vcache), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), B, n_heads, n_kv,
           head_dim, page_size, chunk, n_splits, int(window or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _stream())
     return out
+
+
+# ------------------------------------------------------------------ attention for prompts (bfloat16)
+def attention_prefill_supported(head_dim: int, page_size: int) -> bool:
+    lib = build.load("attention_prefill")
+    f = lib.llm_attention_prefill_supports
+    f.argtypes, f.restype = [c_int, c_int], c_int
+    return bool(f(head_dim, page_size))
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                      seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
+                      max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+                      window: Optional[int], scale: float) -> torch.Tensor:
+    """Causal attention of every sequence's new tokens (rows seq_start[b]..seq_start[b+1]-1 of
+    ``q``, standing behind seq_past[b] cached tokens) over the paged cache, which already
+    holds the new tokens' keys and values."""
+    _on_gpu(q, out, kcache, vcache, seq_start, seq_past, page_table)
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == q.shape[0]
+    assert seq_start.dtype == torch.int32 and seq_past.dtype == torch.int32 and page_table.dtype == torch.int32
+    assert seq_start.numel() >= n_seqs + 1 and seq_past.numel() >= n_seqs and page_table.shape[0] >= n_seqs
+    assert kcache.is_contiguous() and vcache.is_contiguous()
+    assert tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
+    _call("attention_prefill", "llm_attention_prefill",
+          [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+          _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(seq_start),
+          _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv, head_dim,
+          page_size, int(window or 0), float(scale), _stream())
+    return out

@@ -308,3 +308,68 @@ def test_attention_decode(n_heads, n_kv, d, window, chunk, n_splits):
     for b in range(B):
         ref = P.attention_scores_softmax_values(q[b:b + 1].cpu().view(1, n_heads, d), ks[b], vs[b], window)
         close(out[b].view(1, n_heads, d), ref, "bfloat16", scale=1.0)
+
+
+def prefill_inputs(lens, q_lens):
+    start = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    past = torch.tensor([l - n for l, n in zip(lens, q_lens)], dtype=torch.int32, device=DEV)
+    return start, past
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d,window", [(4, 2, 16, None), (3, 1, 48, None), (32, 8, 64, None),
+                                                     (5, 5, 80, None), (8, 2, 128, None), (4, 1, 32, 37),
+                                                     (2, 2, 64, 64), (6, 3, 112, 130)])
+def test_attention_prefill(n_heads, n_kv, d, window):
+    """Whole prompts, the end of a prompt behind cached tokens, tile edges (63, 64, 65 rows) and
+    single tokens in one launch, against the plain attention of each sequence."""
+    from libllm_b200.csrc import ops
+    page = 64
+    lens = [1, 70, 333, 200, 64, 65, 63]
+    q_lens = [1, 70, 5, 150, 64, 65, 1]
+    B = len(lens)
+    K, V, table, ks, vs = paged_cache(B, lens, n_kv, d, page, "bfloat16", 31)
+    T = sum(q_lens)
+    q = rnd((T, n_heads * d), "bfloat16", 32)
+    out = torch.full((T, n_heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    start, past = prefill_inputs(lens, q_lens)
+    assert ops.attention_prefill_supported(d, page)
+    ops.attention_prefill(q, out, K, V, start, past, table, B, max(q_lens), n_heads, n_kv, d, page, window,
+                          1 / math.sqrt(d))
+    o = 0
+    for s, n in enumerate(q_lens):
+        ref = P.attention_scores_softmax_values(q[o:o + n].cpu().view(n, n_heads, d), ks[s], vs[s], window)
+        close(out[o:o + n].view(n, n_heads, d), ref, "bfloat16", scale=1.0)
+        o += n
+
+
+def test_attention_prefill_finds_a_far_key_and_respects_the_window_edge():
+    """Row 700 of a 900-token prompt matches key 3 strongly: without a window key 3's value
+    dominates that row; with a window of 697 key 3 is the last one outside (700 - 697 = 3) and
+    must not be seen, with 698 it is the first one inside."""
+    from libllm_b200.csrc import ops
+    d, page, L = 64, 64, 900
+    K, V, table, ks, vs = paged_cache(1, [L], 1, d, page, "bfloat16", 33)
+    q = rnd((L, d), "bfloat16", 34)
+    k3 = (q[700].float().cpu() * 3.0).to(torch.bfloat16)
+    K[int(table[0, 0]), 0, 3] = k3.to(DEV)
+    ks[0][3, 0] = k3
+    start, past = prefill_inputs([L], [L])
+    for window, sees in ((None, True), (697, False), (698, True)):
+        out = torch.empty((L, d), dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill(q, out, K, V, start, past, table, 1, L, 1, 1, d, page, window, 1 / math.sqrt(d))
+        ref = P.attention_scores_softmax_values(q.cpu().view(L, 1, d), ks[0], vs[0], window)
+        close(out.view(L, 1, d), ref, "bfloat16", scale=1.0)
+        near = float((out[700].float().cpu() - vs[0][3, 0].float()).abs().max()) < 0.2
+        assert near == sees, (window, near)
+
+
+def test_attention_prefill_refuses_what_it_cannot_do():
+    from libllm_b200.csrc import ops
+    from libllm_b200.errors import UnsupportedError
+    assert not ops.attention_prefill_supported(256, 64) and not ops.attention_prefill_supported(64, 16)
+    assert not ops.attention_prefill_supported(40, 64)
+    K, V, table, _, _ = paged_cache(1, [10], 1, 144, 64, "bfloat16", 35)
+    q = rnd((10, 144), "bfloat16", 36)
+    start, past = prefill_inputs([10], [10])
+    with pytest.raises(UnsupportedError):
+        ops.attention_prefill(q, torch.empty_like(q), K, V, start, past, table, 1, 10, 1, 1, 144, 64, None, 0.1)
