@@ -106,15 +106,21 @@ def rope_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) -> to
     return out
 
 
-def rope_rotate(x: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
+def rope_rotate(x: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, table=None) -> torch.Tensor:
     """x*cos + rotate_half(x)*sin with rotate_half(x) = concat(-x[d/2:], x[:d/2]); cos and
     sin rows repeat the d/2 angles twice (src/libllm/llama.cc:151-176).  ``x`` is
     [tokens, heads, d], ``positions`` the absolute position of each token: the tokens
-    already in the sequence come first (src/libllm/llama.cc:188-200)."""
+    already in the sequence come first (src/libllm/llama.cc:188-200).  ``table`` = (cos, sin),
+    each [positions, d], replaces the computed angles: the reference reads such a table from
+    its model file (src/libllm/llama.cc:282-283), and the golden test hands over the same one."""
     x = x.to(DT)
-    angle = positions.to(DT)[:, None] * freqs[None, :]          # [T, d/2]
-    cos = torch.cat([angle.cos(), angle.cos()], dim=-1)[:, None, :]
-    sin = torch.cat([angle.sin(), angle.sin()], dim=-1)[:, None, :]
+    if table is not None:
+        cos = table[0].to(DT)[positions.long()][:, None, :]
+        sin = table[1].to(DT)[positions.long()][:, None, :]
+    else:
+        angle = positions.to(DT)[:, None] * freqs[None, :]          # [T, d/2]
+        cos = torch.cat([angle.cos(), angle.cos()], dim=-1)[:, None, :]
+        sin = torch.cat([angle.sin(), angle.sin()], dim=-1)[:, None, :]
     half = x.shape[-1] // 2
     rotated = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
     return x * cos + rotated * sin
@@ -169,8 +175,8 @@ def attention_block(x, positions, w: Dict[str, torch.Tensor], prefix: str, c: di
     k = linear(x, w[prefix + "k_proj.weight"], w.get(prefix + "k_proj.bias")).view(T, nKV, d)
     v = linear(x, w[prefix + "v_proj.weight"], w.get(prefix + "v_proj.bias")).view(T, nKV, d)
     freqs = rope_frequencies(d, c["rope_theta"], c["rope_scaling"])
-    q = stored(rope_rotate(q, positions, freqs), act_dtype)
-    k = stored(rope_rotate(k, positions, freqs), act_dtype)
+    q = stored(rope_rotate(q, positions, freqs, c.get("rope_table")), act_dtype)
+    k = stored(rope_rotate(k, positions, freqs, c.get("rope_table")), act_dtype)
     v = stored(v, act_dtype)
     o = stored(attention_scores_softmax_values(q, k, v, window), act_dtype)
     return linear(o.reshape(T, nH * d), w[prefix + "o_proj.weight"])
