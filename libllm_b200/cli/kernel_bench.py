@@ -79,6 +79,7 @@ def bench_gemv(args, timer, M=None, N=None, K=None, swiglu=None, name="gemv"):
     import torch
     from ..parts import fast
     M, N, K = M or args.m, N or args.n, K or args.k
+    fast.GEMV_TOKENS = 64                       # time the weight streamer at any size it takes
     swiglu = args.swiglu if swiglu is None else swiglu
     x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)

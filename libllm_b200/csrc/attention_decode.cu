@@ -45,16 +45,45 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
   __shared__ float sm_o[AD_THREADS / 32][G][D];
   __shared__ float sm_m[AD_THREADS / 32][G], sm_l[AD_THREADS / 32][G];
 
+  // Positions and page tables come from the step's descriptor, which is copied to the device
+  // before the step's first kernel starts; the cached keys and values of earlier tokens do
+  // not depend on the kernel before this one either.  So before the wait this CTA looks up
+  // its pages and asks for them to be brought into L2; the queries and the newest token's
+  // key and value (written by the rotation kernel) are read after it.
+  grid_dependents_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = tok_pos[b] + 1;
   const int kstart = window > 0 ? max(0, len - window) : 0;
   const int c0 = split * chunk;
   const int c1 = min(c0 + chunk, len);
-  if (c0 >= len || c1 <= kstart) return;
+  if (c0 >= len || c1 <= kstart) {
+    grid_dependency_wait();
+    return;
+  }
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK, grp = warp * GPW + lane / LPK;
   const int n_heads = n_kv * G;
+
+  // The chunk's page numbers, once, so that no load address waits on another load.
+  extern __shared__ int s_pages[];
+  {
+    const int *pt = page_table + (size_t)b * pt_stride + c0 / page_size;
+    const int n_pg = (c1 - c0 + page_size - 1) / page_size;
+    const int first_pg = (max(kstart, c0) - c0) / page_size;      // pages before the window may be gone
+    const unsigned bytes = (unsigned)page_size * D * 2u;
+    for (int i = threadIdx.x; i < n_pg; i += AD_THREADS) {
+      const int page = pt[i];
+      s_pages[i] = page;
+      if (i >= first_pg && bytes % 16 == 0) {
+        const size_t off = ((size_t)page * n_kv + kvh) * page_size * D;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(kc + off), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vc + off), "r"(bytes) : "memory");
+      }
+    }
+  }
+  grid_dependency_wait();
+  __syncthreads();
 
   float qr[G][8];
 #pragma unroll
@@ -72,14 +101,6 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
 #pragma unroll
     for (int c = 0; c < 8; ++c) acc[h][c] = 0.f;
   }
-  // The chunk's page numbers, once, so that no load address waits on another load.
-  extern __shared__ int s_pages[];
-  {
-    const int *pt = page_table + (size_t)b * pt_stride + c0 / page_size;
-    const int n_pg = (c1 - c0 + page_size - 1) / page_size;
-    for (int i = threadIdx.x; i < n_pg; i += AD_THREADS) s_pages[i] = pt[i];
-  }
-  __syncthreads();
 
   constexpr int STEP = GROUPS * AD_KB;
   auto load = [&](int base, uint4 (&kr)[AD_KB], uint4 (&vr)[AD_KB]) {
@@ -221,6 +242,8 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
                                                 const int *__restrict__ tok_pos, int n_heads, int D, int chunk,
                                                 int window, int n_splits, __nv_bfloat16 *__restrict__ out,
                                                 long long out_stride) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int head = blockIdx.x, b = blockIdx.y;
   const int len = tok_pos[b] + 1;
   const int kstart = window > 0 ? max(0, len - window) : 0;
@@ -245,16 +268,15 @@ static int launch_decode(const void *q, long long q_stride, const void *kc, cons
   dim3 grid(n_splits, n_kv, n_seqs);
   const size_t smem = (size_t)((chunk + page_size - 1) / page_size) * sizeof(int);
   LLM_REQUIRE(smem <= 16 * 1024, "attention_decode: a chunk of %d keys spans too many pages", chunk);
-  attention_decode_kernel<D, G><<<grid, AD_THREADS, smem, stream>>>(
+  llm_launch(attention_decode_kernel<D, G>, grid, dim3(AD_THREADS), smem, stream,
       (const __nv_bfloat16 *)q, q_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, tok_pos, page_table,
       pt_stride, n_kv, page_size, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
       (__nv_bfloat16 *)out, out_stride);
   LLM_CHECK_LAUNCH("attention_decode");
   if (n_splits > 1) {
     dim3 cgrid(n_kv * G, n_seqs);
-    attention_decode_combine_kernel<<<cgrid, D < 64 ? 32 : 64, 0, stream>>>(ws_o, ws_ml, tok_pos, n_kv * G, D, chunk,
-                                                                          window, n_splits, (__nv_bfloat16 *)out,
-                                                                          out_stride);
+    llm_launch(attention_decode_combine_kernel, cgrid, dim3(D < 64 ? 32 : 64), 0, stream, (const float *)ws_o,
+               (const float *)ws_ml, tok_pos, n_kv * G, D, chunk, window, n_splits, (__nv_bfloat16 *)out, out_stride);
     LLM_CHECK_LAUNCH("attention_decode_combine");
   }
   return LLM_OK;

@@ -77,6 +77,8 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
   __nv_bfloat16 *sK = sQ + AP_BM * LD;                       // [2][AP_BN][LD]
   __nv_bfloat16 *sV = sK + 2 * AP_BN * LD;                   // [2][AP_BN][LD]
 
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int b = blockIdx.z, h = blockIdx.y;
   const int q0 = seq_start[b], n_q = seq_start[b + 1] - q0, past = seq_past[b];
   const int tile = gridDim.x - 1 - blockIdx.x;               // long tiles first
@@ -253,10 +255,9 @@ static int launch_prefill(const void *q, long long q_stride, void *out, long lon
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    "attention_prefill attribute");
   dim3 grid((max_q_len + AP_BM - 1) / AP_BM, n_heads, n_seqs);
-  kern<<<grid, AP_WARPS * 32, smem, stream>>>((const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out, out_stride,
-                                              (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, seq_start,
-                                              seq_past, page_table, pt_stride, n_heads, n_kv, window,
-                                              scale * 1.4426950408889634f);
+  llm_launch(kern, grid, dim3(AP_WARPS * 32), smem, stream, (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out,
+             out_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, seq_start, seq_past, page_table,
+             pt_stride, n_heads, n_kv, window, scale * 1.4426950408889634f);
   LLM_CHECK_LAUNCH("attention_prefill");
   return LLM_OK;
 }

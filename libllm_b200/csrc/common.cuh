@@ -54,6 +54,40 @@ static thread_local char g_llm_error[512] = "";
 #define LLM_DEFINE_LAST_ERROR(fn) \
   LLM_EXPORT const char *fn() { return g_llm_error; }
 
+// Programmatic dependent launch.  A kernel launched with `llm_launch` may start while the
+// kernel before it in the stream is still running: its CTAs are scheduled as soon as every
+// CTA of the predecessor has called `grid_dependents_launch` (or has exited).  Before it
+// reads anything an earlier kernel wrote, and before it writes anything an earlier kernel
+// may still read, it calls `grid_dependency_wait`, which returns when the predecessor has
+// finished and its writes are visible.  What a kernel does before the wait (index
+// arithmetic, loads of weights) overlaps the predecessor's tail.  Every thread of every
+// kernel launched this way calls the wait, so completion stays transitive along the stream.
+// Without the launch attribute both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool llm_pdl_enabled() {
+  static const bool on = getenv("LIBLLM_B200_NO_PDL") == nullptr;
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t llm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = llm_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -64,6 +98,23 @@ __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+
+// Four consecutive values as 32-bit floats, from or to either element type.
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16 *p) {
+  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16 *p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned *>(&a);
+  raw.y = *reinterpret_cast<unsigned *>(&b);
+  *reinterpret_cast<uint2 *>(p) = raw;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

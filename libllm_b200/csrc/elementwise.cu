@@ -14,6 +14,8 @@ LLM_DEFINE_LAST_ERROR(llm_elementwise_last_error)
 template <typename T>
 __global__ void embedding_kernel(const T *__restrict__ table, const int *__restrict__ tokens,
                                  float *__restrict__ out, int hidden, int vocab) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int t = blockIdx.x;
   int id = tokens[t];
   // Token ids are checked on the host before they are uploaded; ids that the sampler
@@ -31,9 +33,9 @@ LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, fl
   LLM_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
   int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == LLM_F32)
-    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>((const float *)table, tokens, out, hidden, vocab);
+    llm_launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, out, hidden, vocab);
   else if (dtype == LLM_BF16)
-    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16 *)table, tokens, out, hidden, vocab);
+    llm_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, out, hidden, vocab);
   else
     LLM_FAIL("embedding: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("embedding");
@@ -52,6 +54,8 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ resid, const TD *__restri
                                    int hidden) {
   extern __shared__ float row_buf[];   // hidden floats
   __shared__ float scratch[THREADS / 32 + 1];
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float *x = resid + (size_t)r * hidden;
@@ -70,22 +74,6 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ resid, const TD *__restri
   for (int c = threadIdx.x; c < hidden; c += THREADS) o[c] = from_float<TO>(row_buf[c] * weight[c] * inv);
 }
 
-__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
-__device__ __forceinline__ float4 ld4(const __nv_bfloat16 *p) {
-  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
-  return make_float4(a.x, a.y, b.x, b.y);
-}
-__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
-__device__ __forceinline__ void st4(__nv_bfloat16 *p, float4 v) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-  uint2 raw;
-  raw.x = *reinterpret_cast<unsigned *>(&a);
-  raw.y = *reinterpret_cast<unsigned *>(&b);
-  *reinterpret_cast<uint2 *>(p) = raw;
-}
-
 // The same for rows whose width is a multiple of 4 and at most 4 * VPT * THREADS, with up
 // to MAXP parts: every thread issues all its loads (the row, every part, the weight) before
 // it uses one, so the kernel waits for memory once and not once per part.  The values,
@@ -98,17 +86,25 @@ add_rmsnorm_vec_kernel(float *__restrict__ resid, const TD *__restrict__ delta, 
                        size_t part_stride, const float *__restrict__ weight, float eps,
                        TO *__restrict__ out, const int *__restrict__ rows, int hidden) {
   __shared__ float scratch[THREADS / 32 + 1];
+  grid_dependents_launch();
   const int i = blockIdx.x;
-  const int r = rows ? rows[i] : i;
-  float *x = resid + (size_t)r * hidden;
   const int n4 = hidden / 4;
   float4 v[VPT], w[VPT], d[VPT][MAXP];
+  if (out) {                             // the norm's weight does not depend on the kernel before
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int c4 = threadIdx.x + j * THREADS;
+      if (c4 < n4) w[j] = ld4(weight + 4 * c4);
+    }
+  }
+  grid_dependency_wait();
+  const int r = rows ? rows[i] : i;
+  float *x = resid + (size_t)r * hidden;
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
     const int c4 = threadIdx.x + j * THREADS;
     if (c4 < n4) {
       v[j] = ld4(x + 4 * c4);
-      if (out) w[j] = ld4(weight + 4 * c4);
 #pragma unroll
       for (int p = 0; p < MAXP; ++p)
         if (p < n_parts) d[j][p] = ld4(delta + p * part_stride + (size_t)r * hidden + 4 * c4);
@@ -156,8 +152,8 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
   const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
                        (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
   if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= MAXP) {
-    add_rmsnorm_vec_kernel<TD, TO, THREADS, VPT, MAXP><<<n_rows, THREADS, 0, stream>>>(
-        resid, (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden);
+    llm_launch(add_rmsnorm_vec_kernel<TD, TO, THREADS, VPT, MAXP>, n_rows, THREADS, 0, stream, resid,
+               (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden);
     LLM_CHECK_LAUNCH("add_rmsnorm");
     return LLM_OK;
   }
@@ -168,8 +164,8 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    "add_rmsnorm attribute");
   }
-  kern<<<n_rows, THREADS, smem, stream>>>(resid, (const TD *)delta, n_parts, part_stride, weight, eps,
-                                          (TO *)out, rows, hidden);
+  llm_launch(kern, n_rows, THREADS, smem, stream, resid, (const TD *)delta, n_parts, part_stride, weight, eps,
+             (TO *)out, rows, hidden);
   LLM_CHECK_LAUNCH("add_rmsnorm");
   return LLM_OK;
 }
@@ -200,6 +196,8 @@ LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype,
 // type of the stacked gate|up product (32-bit when the product gives that), T of out.
 template <typename TI, typename T>
 __global__ void swiglu_kernel(const TI *__restrict__ gu, T *__restrict__ out, int inter, size_t total) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
@@ -219,11 +217,11 @@ LLM_EXPORT int llm_swiglu(int in_dtype, int dtype, const void *gu, void *out, in
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (in_dtype == LLM_F32 && dtype == LLM_F32)
-    swiglu_kernel<float, float><<<(unsigned)blocks, threads, 0, stream>>>((const float *)gu, (float *)out, inter, total);
+    llm_launch(swiglu_kernel<float, float>, (unsigned)blocks, threads, 0, stream, (const float *)gu, (float *)out, inter, total);
   else if (in_dtype == LLM_F32 && dtype == LLM_BF16)
-    swiglu_kernel<float, __nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const float *)gu, (__nv_bfloat16 *)out, inter, total);
+    llm_launch(swiglu_kernel<float, __nv_bfloat16>, (unsigned)blocks, threads, 0, stream, (const float *)gu, (__nv_bfloat16 *)out, inter, total);
   else if (in_dtype == LLM_BF16 && dtype == LLM_BF16)
-    swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, inter, total);
+    llm_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, (unsigned)blocks, threads, 0, stream, (const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, inter, total);
   else
     LLM_FAIL("swiglu: unsupported dtypes in %d out %d", in_dtype, dtype);
   LLM_CHECK_LAUNCH("swiglu");

@@ -223,10 +223,16 @@ def gemv_suggest_parts(M: int, N: int, K: int) -> int:
     return int(f(M, N, K))
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+PREFETCH_CAP = 64 << 20      # bytes of the next matrix asked into L2 ahead of its product
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
+              prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64; with ``swiglu`` w is the stacked
     gate|up matrix [2I, K] and out[M, I] = silu(gate) * up.  A 3-d ``out`` [parts, M, N]
-    (32-bit) receives partial products over parts of K, to be added by the caller."""
+    (32-bit) receives partial products over parts of K, to be added by the caller.
+    ``prefetch`` names the matrix the step multiplies by next: its first bytes (up to
+    ``PREFETCH_CAP``) are asked into L2 while this product runs."""
     _on_gpu(x, w, out)
     M, K = x.shape
     N = w.shape[0]
@@ -235,11 +241,17 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool 
         parts, stride = out.shape[0], out.stride(0)
         assert out.dtype == torch.float32 and not swiglu and out.is_contiguous()
     assert w.shape[1] == K and out.stride(-1) == 1 and tuple(out.shape[-2:]) == (M, N // 2 if swiglu else N)
+    pf_bytes = 0
+    if prefetch is not None:
+        _on_gpu(prefetch)
+        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_CAP) // 16 * 16
+        if not prefetch.is_contiguous() or prefetch.data_ptr() % 16:
+            prefetch, pf_bytes = None, 0
     _call("gemv", "llm_gemv_bf16",
           [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
-           c_longlong, c_void_p],
+           c_longlong, c_void_p, c_longlong, c_void_p],
           _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(-2) if M > 1 else out.shape[-1],
-          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _stream())
+          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _ptr(prefetch), pf_bytes, _stream())
     return out
 
 

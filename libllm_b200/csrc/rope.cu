@@ -27,6 +27,8 @@ __global__ void rope_cache_write_kernel(const TI *__restrict__ qkv, long long ro
                                         const int *__restrict__ tok_pos, const int *__restrict__ page_table,
                                         int pt_stride, T *__restrict__ kcache, T *__restrict__ vcache,
                                         int page_size) {
+  grid_dependents_launch();
+  grid_dependency_wait();
   const int t = blockIdx.x;
   const int slot = blockIdx.y;                 // 0..n_heads-1: q, then k heads, then v heads
   const int pos = tok_pos[t];
@@ -59,6 +61,50 @@ __global__ void rope_cache_write_kernel(const TI *__restrict__ qkv, long long ro
   for (int i = rot_dim + threadIdx.x; i < d; i += blockDim.x) dst[i] = from_float<T>(to_float(row[i]));
 }
 
+// The same with four channel pairs per thread and one CTA per token, for head sizes that are
+// a multiple of 8 and rotate all of their channels: 16-byte loads, and the position and the
+// page are looked up once per token.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+rope_cache_write_vec_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out,
+                            long long q_stride, int n_heads, int n_kv, int d, const float *__restrict__ table,
+                            int table_rows, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
+                            const int *__restrict__ page_table, int pt_stride, T *__restrict__ kcache,
+                            T *__restrict__ vcache, int page_size, int n_slots) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = d / 2, groups = half / 4;
+  size_t cache_row = 0;
+  if (n_slots > n_heads) {
+    const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+    cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
+  }
+  const float *cs = table + (size_t)(pos < table_rows ? pos : table_rows - 1) * d;
+  for (int item = threadIdx.x; item < n_slots * groups; item += blockDim.x) {
+    const int slot = item / groups, j = (item % groups) * 4;
+    const TI *row = qkv + (size_t)t * row_stride + (size_t)slot * d;
+    const float4 a = ld4(row + j), b = ld4(row + j + half);
+    const bool is_v = slot >= n_heads + n_kv;
+    T *dst;
+    if (slot < n_heads) {
+      dst = q_out + (size_t)t * q_stride + (size_t)slot * d;
+    } else {
+      const int kvh = is_v ? slot - n_heads - n_kv : slot - n_heads;
+      dst = (is_v ? vcache : kcache) + (cache_row + (size_t)kvh * page_size) * d;
+    }
+    if (is_v) {
+      st4(dst + j, a);
+      st4(dst + j + half, b);
+    } else {
+      const float4 c = ld4(cs + j), s = ld4(cs + half + j);
+      st4(dst + j, make_float4(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y, a.z * c.z - b.z * s.z, a.w * c.w - b.w * s.w));
+      st4(dst + j + half, make_float4(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y, b.z * c.z + a.z * s.z, b.w * c.w + a.w * s.w));
+    }
+  }
+}
+
 // in_dtype: type of qkv; dtype: type of q_out and of the cache.  With write_cache == 0
 // only the query heads are processed (the layer reads another layer's keys and values).
 LLM_EXPORT int llm_rope_cache_write(int in_dtype, int dtype, const void *qkv, long long row_stride,
@@ -71,10 +117,29 @@ LLM_EXPORT int llm_rope_cache_write(int in_dtype, int dtype, const void *qkv, lo
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0, "rope: bad sizes");
   LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim > 0, "rope: rotated width %d does not fit head size %d", rot_dim, d);
   LLM_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope: too many heads for one launch");
-  dim3 grid(n_tokens, write_cache ? n_heads + 2 * n_kv : n_heads);
+  const int n_slots = write_cache ? n_heads + 2 * n_kv : n_heads;
+  const bool vec = d % 8 == 0 && rot_dim == d && row_stride % 4 == 0 && q_stride % 4 == 0 &&
+                   (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)table % 16 == 0 &&
+                   (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0;
+  if (vec) {
+    const int items = n_slots * (d / 8);
+    const int vthreads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+#define ROPE_VEC(TI, T)                                                                                  \
+  llm_launch(rope_cache_write_vec_kernel<TI, T>, dim3(n_tokens), dim3(vthreads), 0, stream, (const TI *)qkv, \
+             row_stride, (T *)q_out, q_stride, n_heads, n_kv, d, table, table_rows, tok_seq, tok_pos,    \
+             page_table, pt_stride, (T *)kcache, (T *)vcache, page_size, n_slots)
+    if (in_dtype == LLM_F32 && dtype == LLM_F32) ROPE_VEC(float, float);
+    else if (in_dtype == LLM_F32 && dtype == LLM_BF16) ROPE_VEC(float, __nv_bfloat16);
+    else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) ROPE_VEC(__nv_bfloat16, __nv_bfloat16);
+    else LLM_FAIL("rope: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef ROPE_VEC
+    LLM_CHECK_LAUNCH("rope_cache_write");
+    return LLM_OK;
+  }
+  dim3 grid(n_tokens, n_slots);
   int threads = d / 2 >= 64 ? 64 : 32;
 #define ROPE_LAUNCH(TI, T)                                                                              \
-  rope_cache_write_kernel<TI, T><<<grid, threads, 0, stream>>>(                                         \
+  llm_launch(rope_cache_write_kernel<TI, T>, grid, dim3(threads), 0, stream,                           \
       (const TI *)qkv, row_stride, (T *)q_out, q_stride, n_heads, n_kv, d, table, table_rows, rot_dim,  \
       tok_seq, tok_pos, page_table, pt_stride, (T *)kcache, (T *)vcache, page_size)
   if (in_dtype == LLM_F32 && dtype == LLM_F32) ROPE_LAUNCH(float, float);

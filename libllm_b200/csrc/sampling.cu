@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(ST) argmax_kernel(const float *__restrict__ lo
                                                     int V, int *__restrict__ out) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  grid_dependents_launch();
+  grid_dependency_wait();
   const ArgMax r = block_argmax(logits + (size_t)blockIdx.x * stride, V, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
@@ -147,6 +149,8 @@ sample_kernel(const float *__restrict__ logits, long long stride, int V, float t
   __shared__ unsigned sel_prefix, sel_mask;
   __shared__ int sel_remaining, n_greater, result;
   __shared__ unsigned long long cand[MAX_TOP_K];
+  grid_dependents_launch();
+  grid_dependency_wait();
 
   const float *row = logits + (size_t)blockIdx.x * stride;
   const int tid = threadIdx.x;
@@ -286,7 +290,7 @@ LLM_EXPORT int llm_argmax(const float *logits, long long stride, int n_rows, int
                           cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
-  argmax_kernel<<<n_rows, ST, 0, stream>>>(logits, stride, vocab, out);
+  llm_launch(argmax_kernel, n_rows, ST, 0, stream, logits, stride, vocab, out);
   LLM_CHECK_LAUNCH("argmax");
   return LLM_OK;
 }
@@ -299,7 +303,7 @@ LLM_EXPORT int llm_sample(const float *logits, long long stride, int n_rows, int
   LLM_REQUIRE(top_k >= 0 && top_k <= MAX_TOP_K, "sample: top_k %d is outside 0..%d", top_k, MAX_TOP_K);
   LLM_REQUIRE(top_p > 0.f, "sample: top_p must be positive");
   LLM_REQUIRE(top_k > 0 || top_p >= 1.f, "sample: top_p below 1 needs a top_k");
-  sample_kernel<<<n_rows, ST, 0, stream>>>(logits, stride, vocab, temperature, top_k, top_p, uniforms, out);
+  llm_launch(sample_kernel, n_rows, ST, 0, stream, logits, stride, vocab, temperature, top_k, top_p, uniforms, out);
   LLM_CHECK_LAUNCH("sample");
   return LLM_OK;
 }

@@ -373,3 +373,32 @@ def test_attention_prefill_refuses_what_it_cannot_do():
     start, past = prefill_inputs([10], [10])
     with pytest.raises(UnsupportedError):
         ops.attention_prefill(q, torch.empty_like(q), K, V, start, past, table, 1, 10, 1, 1, 144, 64, None, 0.1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rope_on_a_part_of_the_channels(dtype):
+    """Only the first 16 of 32 channels rotate (pairs (i, i + 8)); the rest pass through.  This is
+    the general kernel; heads that rotate whole take the vectorised one."""
+    from libllm_b200.csrc import ops
+    n_heads, n_kv, d, rot, page = 2, 1, 32, 16, 8
+    T = 5
+    qkv = rnd((T, (n_heads + 2 * n_kv) * d), dtype, 40)
+    q_out = torch.zeros((T, n_heads * d), dtype=DT[dtype], device=DEV)
+    freqs = torch.tensor([0.5 ** i for i in range(rot // 2)], dtype=torch.float64)
+    ang = torch.arange(16, dtype=torch.float64)[:, None] * freqs[None]
+    table = torch.cat([ang.cos(), ang.sin()], 1).float().to(DEV)
+    tok_seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    tok_pos = torch.arange(3, 3 + T, dtype=torch.int32, device=DEV)
+    pt = torch.tensor([[2, 0, 1, 3]], dtype=torch.int32, device=DEV)
+    K = torch.zeros((4, n_kv, page, d), dtype=DT[dtype], device=DEV)
+    V = torch.zeros_like(K)
+    ops.rope_cache_write(qkv, q_out, n_heads, n_kv, d, table, tok_seq, tok_pos, pt, K, V, page)
+    x = qkv.cpu().view(T, n_heads + 2 * n_kv, d)
+    want = x[:, :n_heads].clone().double()
+    want[..., :rot] = P.rope_rotate(x[:, :n_heads, :rot], tok_pos.cpu().double(), freqs)
+    close(q_out.cpu().view(T, n_heads, d), want, dtype)
+    kwant = x[:, n_heads:n_heads + n_kv].clone().double()
+    kwant[..., :rot] = P.rope_rotate(x[:, n_heads:n_heads + n_kv, :rot], tok_pos.cpu().double(), freqs)
+    for t in range(T):
+        p = 3 + t
+        close(K[int(pt[0, p // page]), :, p % page], kwant[t], dtype)
