@@ -39,6 +39,7 @@ FAMILIES: Dict[str, dict] = {
     "gemv": dict(sources=["gemv.cu"], headers=["common.cuh"]),
     "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh"]),
     "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh"]),
+    "gemm_tc": dict(sources=["gemm_tc.cu"], headers=["common.cuh"]),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

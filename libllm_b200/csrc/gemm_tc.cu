@@ -1,0 +1,528 @@
+// Matrix product on the 5th-generation tensor cores: out[M, N] = x[M, K] * W[N, K]^T, bfloat16
+// operands, 32-bit accumulation in tensor memory, optional fused SwiGLU and partial products
+// over parts of K.  One kernel serves a decoding step of a few tokens, where it streams W once
+// from HBM, and a prompt step of thousands.
+//
+// W's rows are the 128-row operand of tcgen05.mma and the tokens its N operand ("swap AB"): the
+// accumulator of a tile is D[128 rows of W][TN tokens] with TN = 16 .. 256, so that a step of 8
+// tokens costs no more than one of 16 and the instruction shape is full at any batch.  A CTA is
+// persistent (one per SM) and walks over its tiles with three kinds of warps:
+//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of [64 rows x 64 k]
+//            boxes of W and a [TN x 64 k] box of x into a ring of shared-memory stages;
+//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (four k-steps of 16 per stage)
+//            and commits each stage back to the loader and each finished tile to the epilogue;
+//   warps 2-5 read the accumulator with tcgen05.ld (each warp its quarter of the 128 lanes),
+//            apply the epilogue and store out[token][row], while the next tile's products run
+//            into the other accumulator buffer.
+// 90 KB (few tokens) to 200 KB (prompts) of loads are in flight per SM, which is what a stream from
+// HBM needs.
+//
+// SwiGLU: W is the stacked gate|up matrix [2I, K].  A tile holds gate rows f..f+63 in its lanes
+// 0-63 and up rows I+f..I+f+63 in lanes 64-127; the epilogue warps of the upper half hand their
+// values over through shared memory and the lower half stores silu(gate) * up: the stacked
+// product never reaches memory (the reference runs a separate launch, src/flint/cuda/swiglu.cu:29-59,
+// after cuBLAS, src/flint/cuda/gemm_cublas.cc:160-197).
+//
+// Rows of W, tokens and K beyond the matrices are zero-filled by TMA and never stored, so every
+// size is taken (K a multiple of 8: rows must start on 16 bytes).  Every wait on a barrier has a
+// time limit; when it runs out the CTA records a code in `status`, waits for its loads in flight,
+// frees its tensor memory and returns.  Weights are loaded before the programmatic dependency on
+// the previous kernel is waited for, tokens after it.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+LLM_DEFINE_LAST_ERROR(llm_gemm_tc_last_error)
+
+namespace {
+
+constexpr int TC_THREADS = 192;
+constexpr int TC_BK = 64;                      // k per stage: 128 bytes, one swizzle row
+constexpr int TC_ROWS = 128;                   // rows of W per tile (UMMA M)
+constexpr int TC_A_BYTES = TC_ROWS * TC_BK * 2;
+constexpr unsigned long long TC_WAIT_NS = 2000000000ull;   // 2 s
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Waits for the barrier's phase with a time limit.  Returns false when the limit ran out or
+// another warp has given up (`*abort_flag` set); the first to give up records `code`.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, int *status,
+                                          int code) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return mbar_try(bar, parity);
+    if (globaltimer() - t0 > TC_WAIT_NS) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart.  Fields: start address >> 4 (bits 0-13), leading offset (16-29, unused
+// for this layout), stride offset >> 4 (32-45), version 1 (46-47), swizzle mode 2 = 128 B (61-63).
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+  d |= 1ull << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// Instruction descriptor of kind::f16: D in 32-bit floats (bits 4-5 = 1), A and B bfloat16 (bits 7-9
+// and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr unsigned instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+template <int TN>
+struct TcShape {
+  static constexpr int B_BYTES = TN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  // Steps of few tokens (TN <= 64) take half of an SM's shared memory, so that the CTA of the next
+  // product in the stream can move in beside this one and fill its ring with weights while this
+  // one finishes; prompt steps take a ring as deep as fits.
+  static constexpr int BUDGET = TN <= 64 ? 100 * 1024 : 200 * 1024;
+  static constexpr int STAGES = BUDGET / STAGE_BYTES;
+  static constexpr int TMEM_COLS = 2 * TN < 32 ? 32 : 2 * TN;          // two accumulators; a power of two
+  static constexpr int XCH_BYTES = 64 * 17 * 4;                        // SwiGLU hand-over: 64 rows x 16 tokens (+1 pad)
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + XCH_BYTES + 256;
+};
+
+template <int TN, bool SWIGLU, typename TO>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               TO *__restrict__ out, long long ldo, int M, int n_out, int K, int row_tiles, int tok_tiles,
+               int k_parts, int kb_per_part, long long part_stride, int *status) {
+  using S = TcShape<TN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char *xch_raw = smem + (size_t)STAGES * S::STAGE_BYTES;
+  unsigned long long *bars = (unsigned long long *)(xch_raw + S::XCH_BYTES);
+  // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], hand-over full and empty;
+  // then the TMEM address and the abort flag
+  const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
+  const unsigned bar_tfull = smem_u32(bars + 2 * STAGES), bar_tempty = smem_u32(bars + 2 * STAGES + 2);
+  const unsigned bar_xfull = smem_u32(bars + 2 * STAGES + 4), bar_xempty = smem_u32(bars + 2 * STAGES + 5);
+  unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 6);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_dependents_launch();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 4);
+    }
+    mbar_init(bar_xfull, 2);
+    mbar_init(bar_xempty, 2);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((unsigned)S::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  const int n_tiles = row_tiles * tok_tiles * k_parts;
+  const int n_kblocks_total = (K + TC_BK - 1) / TC_BK;
+  constexpr int ROWS_OUT = SWIGLU ? 64 : 128;              // output features per tile
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ loader
+    if (lane == 0) {
+      // The walk over this CTA's (tile, k block) pairs, one per stage filled.
+      struct Walk {
+        int tile, kb, kb1, tok_tile, row_a, row_b;
+        bool valid;
+      };
+      auto start = [&](Walk &w, int tile) {
+        w.tile = tile;
+        w.valid = tile < n_tiles;
+        if (!w.valid) return;
+        const int part = tile % k_parts, row_tile = tile / (k_parts * tok_tiles);
+        w.tok_tile = (tile / k_parts) % tok_tiles;
+        w.kb = part * kb_per_part;
+        w.kb1 = min(n_kblocks_total, w.kb + kb_per_part);
+        w.row_a = row_tile * ROWS_OUT;
+        w.row_b = SWIGLU ? n_out + w.row_a : w.row_a + 64;
+      };
+      auto next = [&](Walk &w) {
+        if (++w.kb >= w.kb1) start(w, w.tile + gridDim.x);
+      };
+      auto load_w = [&](const Walk &w, int stage) {
+        const unsigned dst = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
+        mbar_expect_tx(bar_full + 8 * stage, S::STAGE_BYTES);
+        tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
+        tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
+      };
+      auto load_x = [&](const Walk &w, int stage) {
+        tma_load_2d(smem_u32(smem + (size_t)stage * S::STAGE_BYTES) + TC_A_BYTES, &map_x, w.kb * TC_BK,
+                    w.tok_tile * TN, bar_full + 8 * stage);
+      };
+      // Weights first: they do not depend on the kernel before this one, so the whole ring
+      // is filled with them while that kernel still runs.  Then the wait, then the tokens of
+      // the same stages, then the rest of the walk stage by stage.
+      Walk w, w2;
+      start(w, blockIdx.x);
+      int n_pre = 0;
+      for (; w.valid && n_pre < STAGES; next(w), ++n_pre) load_w(w, n_pre);
+      grid_dependency_wait();
+      start(w2, blockIdx.x);
+      for (int s = 0; s < n_pre; ++s, next(w2)) load_x(w2, s);
+      int stage = n_pre % STAGES;
+      unsigned phase = n_pre == STAGES ? 1u : 0u;
+      bool ok = true;
+      for (; w.valid; next(w)) {
+        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1);
+        if (!ok) break;
+        load_w(w, stage);
+        load_x(w, stage);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok || *abort_flag) {
+        // given up: let the loads that are in flight land before the CTA goes away
+        const unsigned long long t0 = globaltimer();
+        for (int s = 0; s < STAGES; ++s)
+          while (!mbar_try(bar_full + 8 * s, 0) && !mbar_try(bar_full + 8 * s, 1) && globaltimer() - t0 < 2000000ull) {
+          }
+      }
+    } else {
+      grid_dependency_wait();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ tensor-core issue
+    if (lane == 0) {
+      constexpr unsigned IDESC = instr_desc(TC_ROWS, TN);
+      int stage = 0;
+      unsigned phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+        const int part = tile % k_parts;
+        const int kb0 = part * kb_per_part, kb1 = min(n_kblocks_total, kb0 + kb_per_part);
+        const int acc = iter & 1;
+        const unsigned acc_phase = (iter >> 1) & 1;
+        ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned d_tmem = tmem_base + acc * TN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3);
+          if (!ok) break;
+          tc_fence_after();
+          const unsigned a_addr = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
+          const unsigned long long a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + TC_A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < TC_BK / 16; ++kk)    // 16 k = 32 bytes further along the swizzled row
+            tc_mma(d_tmem, a_desc + (unsigned long long)(kk * 2), b_desc + (unsigned long long)(kk * 2), IDESC,
+                   (kb > kb0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar_empty + 8 * stage);          // the stage is free when these products have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(bar_tfull + 8 * acc);      // the tile's accumulator is complete
+      }
+    }
+    grid_dependency_wait();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    grid_dependency_wait();
+    const int quarter = warp & 3;                    // the 32 lanes of tensor memory this warp may read
+    float *xch = (float *)xch_raw;
+    int iter = 0;
+    unsigned n_chunk = 0;                            // hand-overs so far (SwiGLU)
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+      const int part = tile % k_parts, tok_tile = (tile / k_parts) % tok_tiles, row_tile = tile / (k_parts * tok_tiles);
+      const int acc = iter & 1;
+      const unsigned acc_phase = (iter >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 4));
+      if (!ok) break;
+      tc_fence_after();
+      TO *o = out + (size_t)part * part_stride;
+      const int row_in_tile = quarter * 32 + lane;
+      const int tok0 = tok_tile * TN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN && ok; c0 += 16, ++n_chunk) {
+        float v[16];
+        tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * TN + c0), v);
+        if (SWIGLU) {
+          // The upper two warps (up rows) hand their values to the lower two (gate rows of the
+          // same features) through shared memory; both directions are barriers with a time limit.
+          if (quarter >= 2) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_xempty, (n_chunk & 1) ^ 1, abort_flag, status, 5));
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) xch[(row_in_tile - 64) * 17 + i] = v[i];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_xfull);
+          } else {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_xfull, n_chunk & 1, abort_flag, status, 6));
+            if (!ok) break;
+            const int f = row_tile * 64 + row_in_tile;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int tok = tok0 + c0 + i;
+              const float up = xch[row_in_tile * 17 + i];
+              const float g = v[i];
+              if (f < n_out && tok < M) o[(size_t)tok * ldo + f] = from_float<TO>(g / (1.f + expf(-g)) * up);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_xempty);
+          }
+        } else {
+          const int f = row_tile * 128 + row_in_tile;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int tok = tok0 + c0 + i;
+            if (f < n_out && tok < M) o[(size_t)tok * ldo + f] = from_float<TO>(v[i]);
+          }
+        }
+      }
+      if (!ok) break;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- tensor maps (host)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void *ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey &o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    return h * 1000003u ^ (size_t)k.box_rows;
+  }
+};
+
+// A map over a row-major bfloat16 matrix [rows, cols] with row stride ld (elements): boxes of
+// [box_rows x 64] elements, 128-byte swizzle, zeros outside.  Maps are kept: weights come back
+// with every step, and a captured step's activations keep their addresses.
+int get_map(const void *ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap *out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return LLM_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  LLM_REQUIRE(fn != nullptr, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LLM_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed (%d) for a [%lld x %lld] matrix", (int)r, rows, cols);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return LLM_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int TN, bool SWIGLU, typename TO>
+int launch_tc(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N, int K, int k_parts,
+              long long part_stride, int *status, cudaStream_t stream) {
+  using S = TcShape<TN>;
+  const int n_out = SWIGLU ? N / 2 : N;
+  const int rows_out = SWIGLU ? 64 : 128;
+  const int row_tiles = (n_out + rows_out - 1) / rows_out;
+  const int tok_tiles = (M + TN - 1) / TN;
+  const int n_kblocks = (K + TC_BK - 1) / TC_BK;
+  const int kb_per_part = (n_kblocks + k_parts - 1) / k_parts;
+  LLM_REQUIRE((long long)(k_parts - 1) * kb_per_part < n_kblocks, "gemm_tc: %d parts leave one of them without work (K = %d)", k_parts, K);
+  CUtensorMap map_w, map_x;
+  int rc = get_map(W, N, K, K, 64, &map_w);
+  if (rc != LLM_OK) return rc;
+  rc = get_map(x, M, K, ldx, TN, &map_x);
+  if (rc != LLM_OK) return rc;
+  auto kern = gemm_tc_kernel<TN, SWIGLU, TO>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM), "gemm_tc attribute");
+    attr_set = true;
+  }
+  const long long tiles = (long long)row_tiles * tok_tiles * k_parts;
+  LLM_REQUIRE(tiles < (1ll << 30), "gemm_tc: too many tiles");
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  LLM_CHECK_CUDA(llm_launch(kern, dim3(grid), dim3(TC_THREADS), S::SMEM, stream, map_w, map_x, (TO *)out, ldo, M, n_out, K,
+                            row_tiles, tok_tiles, k_parts, kb_per_part, part_stride, status),
+                 "gemm_tc launch");
+  return LLM_OK;
+}
+
+template <bool SWIGLU, typename TO>
+int dispatch_tc(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N, int K, int k_parts,
+                long long part_stride, int *status, cudaStream_t stream) {
+#define TC_GO(TN) return launch_tc<TN, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream)
+  if (M <= 16) TC_GO(16);
+  if (M <= 32) TC_GO(32);
+  if (M <= 64) TC_GO(64);
+  if (M <= 128) TC_GO(128);
+  TC_GO(256);
+#undef TC_GO
+}
+
+}  // namespace
+
+// How many parts of K a product with this few rows of W should be cut into so that most SMs have a
+// tile; 1 when the matrix has tiles enough.  The caller adds the parts (32-bit) in order.
+LLM_EXPORT int llm_gemm_tc_suggest_parts(int M, int N, int K) {
+  const int tok_tiles = M <= 256 ? 1 : (M + 255) / 256;
+  const int tiles = ((N + 127) / 128) * tok_tiles;
+  const int kblocks = (K + TC_BK - 1) / TC_BK;
+  int parts = 1;
+  while (parts < 8 && tiles * parts * 2 <= sm_count() && kblocks / (parts * 2) >= 4) parts *= 2;
+  return parts;
+}
+
+// x [M, K] bfloat16 (row stride ldx elements), W [N, K] bfloat16 contiguous, out [M, N] of out_dtype,
+// or [M, N/2] with swiglu (W = stacked gate|up).  With k_parts > 1 (plain product, 32-bit out) part p
+// writes its share of K to out + p * part_stride.  `status` (device int, may be null) receives a
+// non-zero code if a wait inside the kernel ran out of time.
+LLM_EXPORT int llm_gemm_tc(const void *x, long long ldx, const void *W, void *out, long long ldo, int out_dtype,
+                           int M, int N, int K, int swiglu, int k_parts, long long part_stride, int *status,
+                           cudaStream_t stream) {
+  if (M == 0 || N == 0) return LLM_OK;
+  LLM_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", M, N, K);
+  LLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K = %d and the row stride %lld must be multiples of 8 (rows start on 16 bytes)", K, ldx);
+  LLM_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tc: operands must be 16-byte aligned");
+  LLM_REQUIRE(!swiglu || N % 2 == 0, "gemm_tc: a stacked gate|up matrix has an even number of rows");
+  LLM_REQUIRE(k_parts >= 1 && k_parts <= 64 && (k_parts == 1 || (!swiglu && out_dtype == LLM_F32)),
+              "gemm_tc: parts of K need a plain product with 32-bit output");
+  if (swiglu) {
+    if (out_dtype == LLM_BF16) return dispatch_tc<true, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream);
+    if (out_dtype == LLM_F32) return dispatch_tc<true, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream);
+  } else {
+    if (out_dtype == LLM_BF16) return dispatch_tc<false, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream);
+    if (out_dtype == LLM_F32) return dispatch_tc<false, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream);
+  }
+  LLM_FAIL("gemm_tc: unknown output dtype %d", out_dtype);
+}

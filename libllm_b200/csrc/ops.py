@@ -314,3 +314,60 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
           _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv, head_dim,
           page_size, int(window or 0), float(scale), _stream())
     return out
+
+
+# ------------------------------------------------------------------ product on tcgen05 tensor cores (bfloat16)
+_tc_status = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """The device word in which the tensor-core kernels record that a wait ran out of time."""
+    dev = torch.device(device)
+    t = _tc_status.get(dev)
+    if t is None:
+        t = _tc_status[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return t
+
+
+def check_tc_status() -> None:
+    """Raises if a tensor-core kernel gave up waiting since the last check (this reads the word
+    back, so it waits for the device)."""
+    for dev, t in _tc_status.items():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise ExtensionError(f"a tensor-core kernel on {dev} gave up waiting on a barrier (code {code}: "
+                                 "1 loader, 2-3 issue, 4-6 epilogue); its results are not valid")
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0 and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and (x.shape[0] == 1 or x.stride(0) % 8 == 0) and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_suggest_parts(M: int, N: int, K: int) -> int:
+    lib = build.load("gemm_tc")
+    f = lib.llm_gemm_tc_suggest_parts
+    f.argtypes, f.restype = [c_int, c_int, c_int], c_int
+    return int(f(M, N, K))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T on tcgen05 with TMA-fed operands, for any M; with ``swiglu`` w
+    is the stacked gate|up matrix [2I, K] and out[M, I] = silu(gate) * up.  A 3-d ``out``
+    [parts, M, N] (32-bit) receives partial products over parts of K, to be added by the caller."""
+    _on_gpu(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    parts, stride = 1, 0
+    if out.dim() == 3:
+        parts, stride = out.shape[0], out.stride(0)
+        assert out.dtype == torch.float32 and not swiglu and out.is_contiguous()
+    assert w.shape[1] == K and out.stride(-1) == 1 and tuple(out.shape[-2:]) == (M, N // 2 if swiglu else N)
+    _call("gemm_tc", "llm_gemm_tc",
+          [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
+           c_longlong, c_void_p, c_void_p],
+          _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(-2) if M > 1 else out.shape[-1],
+          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _ptr(tc_status(x.device)), _stream())
+    return out

@@ -402,3 +402,61 @@ def test_rope_on_a_part_of_the_channels(dtype):
     for t in range(T):
         p = 3 + t
         close(K[int(pt[0, p // page]), :, p % page], kwant[t], dtype)
+
+
+TC_SHAPES = [(1, 128, 64), (8, 200, 80), (3, 331, 176), (16, 2048, 2048), (17, 130, 520), (64, 300, 128),
+             (100, 256, 192), (300, 500, 72), (8, 3072, 2048), (2, 64, 8)]
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_tensor_core_product(out_dtype, M, N, K):
+    """Sizes that are no multiple of any tile (rows of W, tokens, K), one token, many tokens."""
+    from libllm_b200.csrc import ops
+    x = rnd((M, K), "bfloat16", 50)
+    w = rnd((N, K), "bfloat16", 51, std=0.1)
+    out = torch.full((M, N), float("nan"), dtype=DT[out_dtype], device=DEV)
+    assert ops.gemm_tc_supported(x, w)
+    ops.gemm_tc(x, w, out)
+    ops.check_tc_status()
+    close(out, P.linear(x.cpu(), w.cpu()), "bfloat16" if out_dtype == "bfloat16" else "float32",
+          scale=None if out_dtype == "bfloat16" else 50 * float(P.linear(x.cpu(), w.cpu()).abs().max()))
+
+
+@pytest.mark.parametrize("M,N,K,parts", [(8, 2048, 2048, 4), (5, 200, 8192, 8), (40, 130, 520, 2), (16, 2048, 8192, 8)])
+def test_tensor_core_product_in_parts_of_k(M, N, K, parts):
+    from libllm_b200.csrc import ops
+    x = rnd((M, K), "bfloat16", 52)
+    w = rnd((N, K), "bfloat16", 53, std=0.1)
+    out = torch.full((parts, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, w, out)
+    ops.check_tc_status()
+    ref = P.linear(x.cpu(), w.cpu())
+    close(out.sum(0), ref, "float32", scale=50 * float(ref.abs().max()))
+    assert 1 <= ops.gemm_tc_suggest_parts(M, N, K) <= 8
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (5, 173, 80), (8, 8192, 2048), (40, 300, 256), (200, 128, 136)])
+def test_tensor_core_product_with_swiglu(M, I, K):
+    from libllm_b200.csrc import ops
+    x = rnd((M, K), "bfloat16", 54)
+    w = rnd((2 * I, K), "bfloat16", 55, std=0.1)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, w, out, swiglu=True)
+    ops.check_tc_status()
+    gu = P.linear(x.cpu(), w.cpu())
+    close(out, P.swiglu(gu[:, :I], gu[:, I:]), "bfloat16")
+
+
+def test_tensor_core_product_rows_do_not_depend_on_the_batch():
+    """A token's row is the same alone and among 200 others: each token is its own column of the tile."""
+    from libllm_b200.csrc import ops
+    x = rnd((200, 256), "bfloat16", 56)
+    w = rnd((384, 256), "bfloat16", 57, std=0.1)
+    full = torch.empty((200, 384), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, w, full)
+    for r in (0, 17, 199):
+        one = torch.empty((1, 384), dtype=torch.float32, device=DEV)
+        ops.gemm_tc(x[r:r + 1].contiguous(), w, one)
+        assert torch.equal(one[0], full[r])
+    ops.check_tc_status()
