@@ -80,6 +80,7 @@ def bench_gemv(args, timer, M=None, N=None, K=None, swiglu=None, name="gemv"):
     from ..parts import fast
     M, N, K = M or args.m, N or args.n, K or args.k
     fast.GEMV_TOKENS = 64                       # time the weight streamer at any size it takes
+    fast.PRODUCT = "gemv"
     swiglu = args.swiglu if swiglu is None else swiglu
     x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
@@ -93,12 +94,21 @@ def bench_gemv(args, timer, M=None, N=None, K=None, swiglu=None, name="gemv"):
             if swiglu:
                 ops.swiglu(y, torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda"))
             return
+        if args.tc:
+            from ..csrc import ops
+            n = N // 2 if swiglu else N
+            parts = 1 if swiglu else ops.gemm_tc_suggest_parts(M, N, K)
+            shape = (M, n) if parts == 1 else (parts, M, n)
+            ops.gemm_tc(x, w, torch.empty(shape, dtype=out_dtype, device="cuda"), swiglu=swiglu)
+            return
         y = fast.small_batch_linear(x, w, out_dtype, swiglu=swiglu, parts_ok=not swiglu)
         assert y is not None, "the small-batch product refused these sizes"
     us = timer.run(fn)
     n_out = N // 2 if swiglu else N
     if args.library:
         name += " (library)"
+    if args.tc:
+        name += " (tcgen05)"
     return report(name, us, bytes_moved=2 * N * K + 2 * M * K + M * n_out * (2 if swiglu else 4),
                   flops=2 * M * N * K, m=M, n=N, k=K, swiglu=bool(swiglu))
 
@@ -230,6 +240,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--tc", action="store_true", help="gemv, layer_products: time the tcgen05 product")
     ap.add_argument("--library", action="store_true", help="gemv, layer_products: time the library product instead")
     ap.add_argument("--generic", action="store_true", help="attention_prefill: time the general kernel")
     ap.add_argument("--iters", type=int, default=20)

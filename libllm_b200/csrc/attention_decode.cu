@@ -46,10 +46,9 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
   __shared__ float sm_m[AD_THREADS / 32][G], sm_l[AD_THREADS / 32][G];
 
   // Positions and page tables come from the step's descriptor, which is copied to the device
-  // before the step's first kernel starts; the cached keys and values of earlier tokens do
-  // not depend on the kernel before this one either.  So before the wait this CTA looks up
-  // its pages and asks for them to be brought into L2; the queries and the newest token's
-  // key and value (written by the rotation kernel) are read after it.
+  // before the step's first kernel starts.  So this CTA looks up its pages before the wait;
+  // the queries and the newest token's key and value (written by the rotation kernel) are
+  // read after it.
   grid_dependents_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = tok_pos[b] + 1;
@@ -70,17 +69,7 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
   {
     const int *pt = page_table + (size_t)b * pt_stride + c0 / page_size;
     const int n_pg = (c1 - c0 + page_size - 1) / page_size;
-    const int first_pg = (max(kstart, c0) - c0) / page_size;      // pages before the window may be gone
-    const unsigned bytes = (unsigned)page_size * D * 2u;
-    for (int i = threadIdx.x; i < n_pg; i += AD_THREADS) {
-      const int page = pt[i];
-      s_pages[i] = page;
-      if (i >= first_pg && bytes % 16 == 0) {
-        const size_t off = ((size_t)page * n_kv + kvh) * page_size * D;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(kc + off), "r"(bytes) : "memory");
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vc + off), "r"(bytes) : "memory");
-      }
-    }
+    for (int i = threadIdx.x; i < n_pg; i += AD_THREADS) s_pages[i] = pt[i];
   }
   grid_dependency_wait();
   __syncthreads();

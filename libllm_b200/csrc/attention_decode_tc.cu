@@ -1,0 +1,364 @@
+// Attention for decoding steps on the tensor cores, with the rotation of q and k, the append
+// of k and v to the paged cache and the joining of the key splits in the same launch.
+//
+// Every sequence brings one token.  CTA (split, kv head, sequence) takes `chunk` cached keys
+// for all query heads of the kv head's group: the group's heads are the rows of one 16-row
+// MMA tile (rows beyond the group are zeros), so S = Q K^T and O += P V are mma.sync m16n8k16
+// products and the issue slots stay free for the loads, which is what this kernel is bound
+// by (it reads K and V once; a kernel that computes the scores on the FMA pipe spends its
+// time issuing).  Key tiles are pages of the cache ([64, d] contiguous) fetched by 16-byte
+// asynchronous copies, two in flight; each of the four warps takes 16 keys of a tile with a
+// running maximum and sum of its own, and the four are joined at the end.
+//
+// What the reference does in some twenty launches per layer (fourteen for the rotation,
+// src/libllm/llama.cc:151-176; two re-allocating appends, :203-212; the split-KV attention and
+// its combine kernel, src/flint/cuda/flash_attn.cc:165-180) is one launch here:
+//  * q's heads are rotated from the 32-bit q|k|v row into the MMA tile; the CTA whose keys
+//    include the new token rotates k, writes k and v to the cache and puts them into its tile;
+//  * each CTA writes its split's unnormalised output, maximum and sum to scratch, and the
+//    CTA that finishes last for a (sequence, kv head) joins the splits in split order, so the
+//    result does not depend on which one that is.
+// Head h reads kv head h / (heads / kv_heads); scores are scaled by `scale` (1/sqrt(d),
+// src/flint/operators.cc:43-56, 115-117); one query sees every cached key or the last `window`.
+#include "common.cuh"
+#include "mma_tiles.cuh"
+#include <math.h>
+
+LLM_DEFINE_LAST_ERROR(llm_attention_decode_tc_last_error)
+
+constexpr int DT_WARPS = 4;
+constexpr int DT_BN = 64;      // keys per tile = tokens per page
+constexpr int DT_ROWS = 16;    // rows of the MMA tile: query heads of one group
+
+template <int D>
+__global__ void __launch_bounds__(DT_WARPS * 32)
+attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, const float *__restrict__ table,
+                           int table_rows, int rot_dim, const int *__restrict__ tok_pos,
+                           const int *__restrict__ page_table, int pt_stride, __nv_bfloat16 *__restrict__ kc,
+                           __nv_bfloat16 *__restrict__ vc, int write_cache, int n_heads, int n_kv, int G, int chunk,
+                           int window, float scale_log2, float *__restrict__ ws_o, float *__restrict__ ws_ml,
+                           int *__restrict__ counters, int n_splits, __nv_bfloat16 *__restrict__ out,
+                           long long out_stride) {
+  constexpr int LD = D + 8;
+  constexpr int CHUNKS = D / 8;
+  constexpr int KS = D / 16;
+  constexpr int DT = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16 *sQ = reinterpret_cast<__nv_bfloat16 *>(smem_raw);           // [16][LD]
+  __nv_bfloat16 *sNew = sQ + DT_ROWS * LD;                                    // [2][LD]: new k, new v
+  __nv_bfloat16 *sK = sNew + 2 * LD;                                          // [2][64][LD]
+  __nv_bfloat16 *sV = sK + 2 * DT_BN * LD;                                    // [2][64][LD]
+  int *s_pages = reinterpret_cast<int *>(sV + 2 * DT_BN * LD);
+  __shared__ float sm_m[DT_WARPS][DT_ROWS], sm_l[DT_WARPS][DT_ROWS];
+  __shared__ int s_last;
+
+  grid_dependents_launch();
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int pos = tok_pos[b];
+  const int len = pos + 1;
+  const int kstart = window > 0 ? max(0, len - window) : 0;
+  const int c0 = split * chunk;
+  const int c1 = min(c0 + chunk, len);
+  if (c0 >= len || c1 <= kstart) {
+    grid_dependency_wait();
+    return;
+  }
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int first_tile = max(c0, kstart) / DT_BN, last_tile = (c1 - 1) / DT_BN;
+  {
+    const int *pt = page_table + (size_t)b * pt_stride;
+    for (int i = first_tile + tid; i <= last_tile; i += DT_WARPS * 32) s_pages[i - first_tile] = pt[i];
+  }
+  const bool owns_new = write_cache && pos >= c0 && pos < c1;     // c1 = len here
+  const int half = rot_dim / 2;
+  const float *cs = table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim;
+  grid_dependency_wait();
+  __syncthreads();
+
+  auto load_kv = [&](int kt, int stage) {
+    const int page = s_pages[kt - first_tile];
+    const size_t base = ((size_t)page * n_kv + kvh) * DT_BN * D;
+    __nv_bfloat16 *dk = sK + stage * DT_BN * LD, *dv = sV + stage * DT_BN * LD;
+    for (int c = tid; c < DT_BN * CHUNKS; c += DT_WARPS * 32) {
+      const int r = c / CHUNKS, ch = c % CHUNKS;
+      cp_async16(dk + r * LD + ch * 8, kc + base + (size_t)r * D + ch * 8, true);
+      cp_async16(dv + r * LD + ch * 8, vc + base + (size_t)r * D + ch * 8, true);
+    }
+  };
+  load_kv(first_tile, 0);
+  cp_async_commit();
+
+  // The group's queries, rotated, as rows of the MMA tile; rows beyond the group are zeros.
+  const float *row = qkv + (size_t)b * qkv_stride;
+  for (int i = tid; i < DT_ROWS * D; i += DT_WARPS * 32) {
+    const int h = i / D, c = i % D;
+    float v = 0.f;
+    if (h < G) {
+      const float *qh = row + (size_t)(kvh * G + h) * D;
+      if (c < half) v = qh[c] * cs[c] - qh[c + half] * cs[half + c];
+      else if (c < rot_dim) v = qh[c] * cs[c - half] + qh[c - half] * cs[c];
+      else v = qh[c];
+    }
+    sQ[h * LD + c] = __float2bfloat16_rn(v);
+  }
+  // The new token's key (rotated) and value: into the cache, and kept for this CTA's own tile.
+  if (owns_new) {
+    const float *kh = row + (size_t)(n_heads + kvh) * D, *vh = row + (size_t)(n_heads + n_kv + kvh) * D;
+    const int page = s_pages[pos / DT_BN - first_tile];
+    const size_t dst = (((size_t)page * n_kv + kvh) * DT_BN + (pos % DT_BN)) * D;
+    for (int c = tid; c < D; c += DT_WARPS * 32) {
+      float kv;
+      if (c < half) kv = kh[c] * cs[c] - kh[c + half] * cs[half + c];
+      else if (c < rot_dim) kv = kh[c] * cs[c - half] + kh[c - half] * cs[c];
+      else kv = kh[c];
+      const __nv_bfloat16 kb = __float2bfloat16_rn(kv), vb = __float2bfloat16_rn(vh[c]);
+      sNew[c] = kb;
+      sNew[LD + c] = vb;
+      kc[dst + c] = kb;
+      vc[dst + c] = vb;
+    }
+  }
+
+  unsigned qf[KS][4];
+  float o[DT][4];
+#pragma unroll
+  for (int i = 0; i < DT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int kt = first_tile; kt <= last_tile; ++kt) {
+    const int stage = (kt - first_tile) & 1;
+    if (kt + 1 <= last_tile) load_kv(kt + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    __nv_bfloat16 *tk = sK + stage * DT_BN * LD, *tv = sV + stage * DT_BN * LD;
+    if (owns_new && kt == pos / DT_BN) {
+      // the copy may have fetched this row before the new token was written: put it in by hand
+      const int r = pos % DT_BN;
+      for (int c = tid; c < D; c += DT_WARPS * 32) {
+        tk[r * LD + c] = sNew[c];
+        tv[r * LD + c] = sNew[LD + c];
+      }
+      __syncthreads();
+    }
+    if (kt == first_tile) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], sQ + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8);
+    }
+    // this warp's 16 keys of the tile
+    const int k0 = kt * DT_BN + warp * 16;
+    if (k0 < c1 && k0 + 16 > kstart) {
+      float s[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[n][j] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        unsigned kb[4];
+        ldmatrix_x4(kb, tk + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma16816(s[0], qf[ks], kb[0], kb[1]);
+        mma16816(s[1], qf[ks], kb[2], kb[3]);
+      }
+      if (k0 + 16 > c1 || k0 < kstart) {
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int key = k0 + n * 8 + 2 * t + (j & 1);
+            if (key >= c1 || key < kstart) s[n][j] = -INFINITY;
+          }
+      }
+      float mx[2];
+      mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      float alpha[2], moff[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        moff[r] = m_new == -INFINITY ? 0.f : m_new * scale_log2;
+        alpha[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] * scale_log2 - moff[r]);
+        m_run[r] = m_new;
+      }
+      float sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        s[n][0] = exp2f(fmaf(s[n][0], scale_log2, -moff[0]));
+        s[n][1] = exp2f(fmaf(s[n][1], scale_log2, -moff[0]));
+        s[n][2] = exp2f(fmaf(s[n][2], scale_log2, -moff[1]));
+        s[n][3] = exp2f(fmaf(s[n][3], scale_log2, -moff[1]));
+        sum[0] += s[n][0] + s[n][1];
+        sum[1] += s[n][2] + s[n][3];
+      }
+      l_run[0] = l_run[0] * alpha[0] + sum[0];
+      l_run[1] = l_run[1] * alpha[1] + sum[1];
+#pragma unroll
+      for (int i = 0; i < DT; ++i) {
+        o[i][0] *= alpha[0];
+        o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1];
+        o[i][3] *= alpha[1];
+      }
+      unsigned pa[4];
+      pa[0] = pack_bf16(s[0][0], s[0][1]);
+      pa[1] = pack_bf16(s[0][2], s[0][3]);
+      pa[2] = pack_bf16(s[1][0], s[1][1]);
+      pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+      for (int d2 = 0; d2 < DT / 2; ++d2) {
+        unsigned vb[4];
+        ldmatrix_x4_trans(vb, tv + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + d2 * 16 + (lane >> 4) * 8);
+        mma16816(o[2 * d2], pa, vb[0], vb[1]);
+        mma16816(o[2 * d2 + 1], pa, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // Join the four warps (each saw other keys): through shared memory, in warp order.
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float *sm_o = reinterpret_cast<float *>(sK);                 // [4][16][D], over the tiles (no longer read)
+  {
+    const int ra = g, rb = g + 8;
+    if (t == 0) {
+      sm_m[warp][ra] = m_run[0] == -INFINITY ? -INFINITY : m_run[0] * scale_log2;
+      sm_m[warp][rb] = m_run[1] == -INFINITY ? -INFINITY : m_run[1] * scale_log2;
+      sm_l[warp][ra] = l_run[0];
+      sm_l[warp][rb] = l_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < DT; ++i) {
+      float *pa = sm_o + ((size_t)(warp * DT_ROWS + ra) * D + i * 8 + 2 * t);
+      float *pb = sm_o + ((size_t)(warp * DT_ROWS + rb) * D + i * 8 + 2 * t);
+      pa[0] = o[i][0];
+      pa[1] = o[i][1];
+      pb[0] = o[i][2];
+      pb[1] = o[i][3];
+    }
+  }
+  __syncthreads();
+  const int n_active_first = kstart / chunk, n_active_last = (len - 1) / chunk;
+  const int n_active = n_active_last - n_active_first + 1;
+  for (int idx = tid; idx < G * D; idx += DT_WARPS * 32) {
+    const int h = idx / D, c = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DT_WARPS; ++w) M = fmaxf(M, sm_m[w][h]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < DT_WARPS; ++w) {
+      const float f = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - M);
+      L += sm_l[w][h] * f;
+      O += sm_o[(size_t)(w * DT_ROWS + h) * D + c] * f;
+    }
+    const int head = kvh * G + h;
+    if (n_active == 1) {
+      out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L);
+    } else {
+      const size_t slot = ((size_t)b * n_heads + head) * n_splits + split;
+      ws_o[slot * D + c] = O;
+      if (c == 0) {
+        ws_ml[slot * 2] = M;
+        ws_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+  if (n_active == 1) return;
+
+  // The CTA that is last to finish for this (sequence, kv head) joins the splits.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[b * n_kv + kvh], 1);
+    s_last = old == n_active - 1;
+    if (s_last) counters[b * n_kv + kvh] = 0;          // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = tid; idx < G * D; idx += DT_WARPS * 32) {
+    const int h = idx / D, c = idx % D;
+    const int head = kvh * G + h;
+    const size_t slot0 = ((size_t)b * n_heads + head) * n_splits;
+    float M = -INFINITY;
+    for (int s = n_active_first; s <= n_active_last; ++s) M = fmaxf(M, __ldcg(ws_ml + (slot0 + s) * 2));
+    float L = 0.f, O = 0.f;
+    for (int s = n_active_first; s <= n_active_last; ++s) {
+      const float f = exp2f(__ldcg(ws_ml + (slot0 + s) * 2) - M);
+      L += __ldcg(ws_ml + (slot0 + s) * 2 + 1) * f;
+      O += __ldcg(ws_o + (slot0 + s) * D + c) * f;
+    }
+    out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L);
+  }
+}
+
+template <int D>
+static int launch_decode_tc(const float *qkv, long long qkv_stride, const float *table, int table_rows, int rot_dim,
+                            const int *tok_pos, const int *page_table, int pt_stride, void *kc, void *vc,
+                            int write_cache, int n_seqs, int n_heads, int n_kv, int chunk, int n_splits, int window,
+                            float scale, float *ws_o, float *ws_ml, int *counters, void *out, long long out_stride,
+                            cudaStream_t stream) {
+  constexpr int LD = D + 8;
+  const size_t tiles = (size_t)(DT_ROWS + 2 + 4 * DT_BN) * LD * sizeof(__nv_bfloat16);
+  const size_t smem = tiles + (size_t)(chunk / DT_BN + 2) * sizeof(int);
+  LLM_REQUIRE(smem <= 200 * 1024, "attention_decode_tc: a chunk of %d keys spans too many pages", chunk);
+  auto kern = attention_decode_tc_kernel<D>;
+  if (smem > 48 * 1024)
+    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   "attention_decode_tc attribute");
+  dim3 grid(n_splits, n_kv, n_seqs);
+  LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(DT_WARPS * 32), smem, stream, qkv, qkv_stride, table, table_rows, rot_dim,
+                            tok_pos, page_table, pt_stride, (__nv_bfloat16 *)kc, (__nv_bfloat16 *)vc, write_cache,
+                            n_heads, n_kv, n_heads / n_kv, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml,
+                            counters, n_splits, (__nv_bfloat16 *)out, out_stride),
+                 "attention_decode_tc launch");
+  return LLM_OK;
+}
+
+// 1 if this head size, page size and group size have an instantiation, else 0.
+LLM_EXPORT int llm_attention_decode_tc_supports(int d, int page_size, int group) {
+  return page_size == DT_BN && d >= 16 && d <= 128 && d % 16 == 0 && group >= 1 && group <= DT_ROWS;
+}
+
+// qkv [B, (heads + 2 kv_heads) * d] 32-bit (the stacked product, not rotated), table
+// [positions, rot_dim] (cosines, then sines), caches [pages, kv_heads, 64, d] bfloat16, tok_pos[b]
+// the position of sequence b's token.  With write_cache the token's k and v are appended.
+// ws_o needs B*heads*n_splits*d floats, ws_ml B*heads*n_splits*2, counters B*kv_heads ints that are
+// zero before the first launch (the kernel leaves them zero).
+LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, const float *table, int table_rows,
+                                       int rot_dim, const int *tok_pos, const int *page_table, int pt_stride,
+                                       void *kc, void *vc, int write_cache, int n_seqs, int n_heads, int n_kv, int d,
+                                       int page_size, int chunk, int n_splits, int window, float scale, float *ws_o,
+                                       float *ws_ml, int *counters, void *out, long long out_stride,
+                                       cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv > 0 && n_kv <= 65535 && n_heads % n_kv == 0,
+              "attention_decode_tc: bad sizes");
+  LLM_REQUIRE(llm_attention_decode_tc_supports(d, page_size, n_heads / n_kv),
+              "attention_decode_tc: head size %d, pages of %d, %d query heads per kv head is not built", d, page_size,
+              n_heads / n_kv);
+  LLM_REQUIRE(chunk > 0 && chunk % page_size == 0 && n_splits >= 1,
+              "attention_decode_tc: chunk %d must be a positive multiple of the page size", chunk);
+  LLM_REQUIRE(rot_dim > 0 && rot_dim % 2 == 0 && rot_dim <= d, "attention_decode_tc: rotated width %d does not fit head size %d", rot_dim, d);
+  LLM_REQUIRE(n_splits == 1 || (ws_o && ws_ml && counters), "attention_decode_tc: splits need scratch memory");
+  LLM_REQUIRE((uintptr_t)kc % 16 == 0 && (uintptr_t)vc % 16 == 0 && (uintptr_t)out % 4 == 0 && out_stride % 2 == 0,
+              "attention_decode_tc: caches must be 16-byte aligned");
+#define DT_CASE(DD)                                                                                                 \
+  if (d == DD)                                                                                                      \
+    return launch_decode_tc<DD>(qkv, qkv_stride, table, table_rows, rot_dim, tok_pos, page_table, pt_stride, kc, vc, \
+                                write_cache, n_seqs, n_heads, n_kv, chunk, n_splits, window, scale, ws_o, ws_ml,    \
+                                counters, out, out_stride, stream);
+  DT_CASE(16) DT_CASE(32) DT_CASE(48) DT_CASE(64) DT_CASE(80) DT_CASE(96) DT_CASE(112) DT_CASE(128)
+#undef DT_CASE
+  LLM_FAIL("attention_decode_tc: no kernel for head size %d", d);
+}

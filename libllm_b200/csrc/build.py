@@ -38,8 +38,9 @@ FAMILIES: Dict[str, dict] = {
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
     "gemv": dict(sources=["gemv.cu"], headers=["common.cuh"]),
     "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh"]),
-    "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh"]),
+    "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "gemm_tc": dict(sources=["gemm_tc.cu"], headers=["common.cuh"]),
+    "attention_decode_tc": dict(sources=["attention_decode_tc.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -148,7 +148,7 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
                               const float *weight, float eps, void *out, const int *rows, int n_rows,
                               int hidden, cudaStream_t stream) {
   constexpr int THREADS = 256;
-  constexpr int VPT = 4, MAXP = 4;
+  constexpr int VPT = 4, MAXP = 8;
   const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
                        (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
   if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= MAXP) {

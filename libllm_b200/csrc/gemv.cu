@@ -45,7 +45,7 @@ template <int NT, int MT, int UNROLL, bool SWIGLU, typename TO>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloat16 *__restrict__ W,
             TO *__restrict__ out, long long ldo, int M, int N, int K, int k_split, int kb_per_part,
-            long long part_stride, const char *__restrict__ next_w, long long next_bytes) {
+            long long part_stride) {
   constexpr int SETS = SWIGLU ? 2 : 1;
   extern __shared__ float red[];          // [k_split][row_groups][SETS*MT*NT*4][32]
   grid_dependents_launch();
@@ -106,36 +106,8 @@ gemv_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloa
             a[u][s][m][h] = kok ? ld_stream16(wrow[s][m][h] + k) : make_uint4(0, 0, 0, 0);
     }
   };
-  // The weights do not depend on the kernel before this one.  While that kernel (and, since
-  // every kernel lets its successor start at once, the ones before it) still runs, this CTA
-  // asks for all of its rows to be brought into L2, one bulk prefetch per row, and issues the
-  // first round's loads; the tokens are read after the wait.  The stream of weights from
-  // HBM thus goes on under the short kernels between two products.
-  {
-    const int k_lo = kb_first * 32, k_hi = min(K, n_kblocks * 32);
-    const int rows_cta = row_groups * 16 * MT;
-    const int cta_row0 = blockIdx.x * rows_cta;
-    const unsigned bytes = (unsigned)(k_hi - k_lo) * 2u;
-    for (int i = threadIdx.x; i < rows_cta * SETS; i += GEMV_WARPS * 32) {
-      const int r = cta_row0 + i % rows_cta, s = i / rows_cta;
-      if (r < n_out && bytes > 0) {
-        const __nv_bfloat16 *p = W + ((size_t)r + (size_t)s * n_out) * K + k_lo;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-      }
-    }
-  }
-  // The matrix that the step multiplies by next (if the caller names one) is asked into L2
-  // as well, a slice per CTA: by the time the next product starts, its weights have crossed
-  // from HBM under this product and the short kernels in between.
-  if (next_bytes > 0) {
-    const long long n_cta = (long long)gridDim.x * gridDim.y, cta = (long long)blockIdx.y * gridDim.x + blockIdx.x;
-    const long long per = ((next_bytes + n_cta - 1) / n_cta + 4095) & ~4095LL;
-    const long long lo = cta * per, hi = min(next_bytes, lo + per);
-    for (long long o = lo + (long long)threadIdx.x * 4096; o < hi; o += (long long)GEMV_WARPS * 32 * 4096) {
-      const unsigned nb = (unsigned)min(4096LL, hi - o);
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(next_w + o), "r"(nb) : "memory");
-    }
-  }
+  // The weights do not depend on the kernel before this one: the first round's loads are
+  // in flight while that kernel drains; the tokens are read after the wait.
   const int kb_begin = kb_first + ks * UNROLL;
   if (kb_begin < n_kblocks) load_weights(kb_begin);
   grid_dependency_wait();
@@ -218,8 +190,7 @@ gemv_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloa
 
 template <int NT, int MT, int UNROLL, bool SWIGLU, typename TO>
 static int launch_gemv(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N,
-                       int K, int k_parts, long long part_stride, const void *next_w, long long next_bytes,
-                       cudaStream_t stream) {
+                       int K, int k_parts, long long part_stride, cudaStream_t stream) {
   constexpr int SETS = SWIGLU ? 2 : 1;
   const int n_out = SWIGLU ? N / 2 : N;
   const int kb_per_part = ((K + 31) / 32 + k_parts - 1) / k_parts;
@@ -240,20 +211,18 @@ static int launch_gemv(const void *x, long long ldx, const void *W, void *out, l
   if (smem > 48 * 1024)
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv attribute");
   llm_launch(kern, dim3(grid, k_parts), dim3(GEMV_WARPS * 32), smem, stream, (const __nv_bfloat16 *)x, ldx,
-             (const __nv_bfloat16 *)W, (TO *)out, ldo, M, N, K, k_split, kb_per_part, part_stride,
-             (const char *)next_w, next_bytes);
+             (const __nv_bfloat16 *)W, (TO *)out, ldo, M, N, K, k_split, kb_per_part, part_stride);
   LLM_CHECK_LAUNCH("gemv");
   return LLM_OK;
 }
 
 template <bool SWIGLU, typename TO>
 static int dispatch_gemv(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N,
-                         int K, int k_parts, long long part_stride, const void *next_w, long long next_bytes,
-                         cudaStream_t stream) {
-  if (M <= 8) return launch_gemv<1, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
-  if (M <= 16) return launch_gemv<2, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
-  if (M <= 32) return launch_gemv<4, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
-  return launch_gemv<8, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
+                         int K, int k_parts, long long part_stride, cudaStream_t stream) {
+  if (M <= 8) return launch_gemv<1, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+  if (M <= 16) return launch_gemv<2, 1, 4, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+  if (M <= 32) return launch_gemv<4, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+  return launch_gemv<8, 1, 2, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
 }
 
 // How many parts of K a product of this shape is best cut into so that the GPU has
@@ -273,7 +242,7 @@ LLM_EXPORT int llm_gemv_suggest_parts(int M, int N, int K) {
 // writes to out + p * part_stride; the sum over parts is the product.
 LLM_EXPORT int llm_gemv_bf16(const void *x, long long ldx, const void *W, void *out, long long ldo, int out_dtype,
                              int M, int N, int K, int swiglu, int k_parts, long long part_stride,
-                             const void *next_w, long long next_bytes, cudaStream_t stream) {
+                             cudaStream_t stream) {
   if (M == 0) return LLM_OK;
   LLM_REQUIRE(M > 0 && M <= 64, "gemv: %d tokens (1..64 are taken)", M);
   LLM_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0, "gemv: K=%d and the row stride must be multiples of 8", K);
@@ -281,15 +250,12 @@ LLM_EXPORT int llm_gemv_bf16(const void *x, long long ldx, const void *W, void *
   LLM_REQUIRE(k_parts >= 1 && k_parts <= 64 && (k_parts == 1 || (!swiglu && out_dtype == LLM_F32)),
               "gemv: parts of K need a plain product with 32-bit output");
   LLM_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemv: operands must be 16-byte aligned");
-  if (!next_w) next_bytes = 0;
-  LLM_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && (uintptr_t)next_w % 16 == 0,
-              "gemv: the matrix to prefetch must be 16-byte aligned and a multiple of 16 bytes");
   if (swiglu) {
-    if (out_dtype == LLM_BF16) return dispatch_gemv<true, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
-    if (out_dtype == LLM_F32) return dispatch_gemv<true, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
+    if (out_dtype == LLM_BF16) return dispatch_gemv<true, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+    if (out_dtype == LLM_F32) return dispatch_gemv<true, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
   } else {
-    if (out_dtype == LLM_BF16) return dispatch_gemv<false, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
-    if (out_dtype == LLM_F32) return dispatch_gemv<false, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, next_w, next_bytes, stream);
+    if (out_dtype == LLM_BF16) return dispatch_gemv<false, __nv_bfloat16>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
+    if (out_dtype == LLM_F32) return dispatch_gemv<false, float>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, stream);
   }
   LLM_FAIL("gemv: unknown output dtype %d", out_dtype);
 }

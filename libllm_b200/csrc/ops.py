@@ -223,16 +223,10 @@ def gemv_suggest_parts(M: int, N: int, K: int) -> int:
     return int(f(M, N, K))
 
 
-PREFETCH_CAP = 64 << 20      # bytes of the next matrix asked into L2 ahead of its product
-
-
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
-              prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64; with ``swiglu`` w is the stacked
     gate|up matrix [2I, K] and out[M, I] = silu(gate) * up.  A 3-d ``out`` [parts, M, N]
-    (32-bit) receives partial products over parts of K, to be added by the caller.
-    ``prefetch`` names the matrix the step multiplies by next: its first bytes (up to
-    ``PREFETCH_CAP``) are asked into L2 while this product runs."""
+    (32-bit) receives partial products over parts of K, to be added by the caller."""
     _on_gpu(x, w, out)
     M, K = x.shape
     N = w.shape[0]
@@ -241,17 +235,11 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool 
         parts, stride = out.shape[0], out.stride(0)
         assert out.dtype == torch.float32 and not swiglu and out.is_contiguous()
     assert w.shape[1] == K and out.stride(-1) == 1 and tuple(out.shape[-2:]) == (M, N // 2 if swiglu else N)
-    pf_bytes = 0
-    if prefetch is not None:
-        _on_gpu(prefetch)
-        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_CAP) // 16 * 16
-        if not prefetch.is_contiguous() or prefetch.data_ptr() % 16:
-            prefetch, pf_bytes = None, 0
     _call("gemv", "llm_gemv_bf16",
           [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
-           c_longlong, c_void_p, c_longlong, c_void_p],
+           c_longlong, c_void_p],
           _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(-2) if M > 1 else out.shape[-1],
-          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _ptr(prefetch), pf_bytes, _stream())
+          dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _stream())
     return out
 
 
@@ -370,4 +358,44 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = 
            c_longlong, c_void_p, c_void_p],
           _ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), out.stride(-2) if M > 1 else out.shape[-1],
           dtype_code(out.dtype), M, N, K, 1 if swiglu else 0, parts, stride, _ptr(tc_status(x.device)), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ decode attention on tensor cores, rotation fused
+def attention_decode_tc_supported(head_dim: int, page_size: int, group: int) -> bool:
+    lib = build.load("attention_decode_tc")
+    f = lib.llm_attention_decode_tc_supports
+    f.argtypes, f.restype = [c_int, c_int, c_int], c_int
+    return bool(f(head_dim, page_size, group))
+
+
+def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tensor, kcache: torch.Tensor,
+                        vcache: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int,
+                        n_kv: int, head_dim: int, page_size: int, chunk: int, n_splits: int, window: Optional[int],
+                        scale: float, write_cache: bool, ws_o: Optional[torch.Tensor],
+                        ws_ml: Optional[torch.Tensor], counters: Optional[torch.Tensor]) -> torch.Tensor:
+    """One token per sequence: rotates q and k of the 32-bit stacked rows ``qkv``, appends k and v to
+    the cache (with ``write_cache``), attends over the cache and joins the key splits, in one launch.
+    ``counters`` (int32, one per sequence and kv head) must be zero before the first launch; the
+    kernel leaves it zero."""
+    _on_gpu(qkv, out, table, kcache, vcache, tok_pos, page_table, ws_o, ws_ml, counters)
+    B = qkv.shape[0]
+    assert qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1
+    assert qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+    assert kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.dim() == 2
+    assert tok_pos.dtype == torch.int32 and tok_pos.numel() >= B and page_table.dtype == torch.int32
+    if n_splits > 1:
+        assert ws_o.dtype == torch.float32 and ws_o.numel() >= B * n_heads * n_splits * head_dim
+        assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
+        assert counters.dtype == torch.int32 and counters.numel() >= B * n_kv
+    _call("attention_decode_tc", "llm_attention_decode_tc",
+          [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+           c_longlong, c_void_p],
+          _ptr(qkv), qkv.stride(0) if B > 1 else qkv.shape[1], _ptr(table), table.shape[0], table.shape[1],
+          _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache), 1 if write_cache else 0,
+          B, n_heads, n_kv, head_dim, page_size, chunk, n_splits, int(window or 0), float(scale), _ptr(ws_o),
+          _ptr(ws_ml), _ptr(counters), _ptr(out), out.stride(0) if B > 1 else out.shape[1], _stream())
     return out

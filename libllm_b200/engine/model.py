@@ -54,7 +54,6 @@ class Model:
                 raise ConfigError(f"schedule entry {i} reads the cache of entry {e.cache_from}, which does not run before it")
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
-        self.weight_after: Dict[int, torch.Tensor] = {}
 
     # ---------------------------------------------------------------- weights
     def tensor_needs(self) -> List[TensorNeed]:
@@ -84,15 +83,10 @@ class Model:
             layer.load(fetch)
         self.final_norm.load(fetch)
         self.head = self.embedding if s.head is None else fetch(needs[-1])
-        # Every matrix the step multiplies by, in the order it does: w -> the one after it.
-        chain = [w for e in s.schedule for w in self.layers[e.layer].streamed_weights()] + [self.head]
-        self.weight_after = {}
-        for a, b in zip(chain, chain[1:]):
-            self.weight_after.setdefault(a.data_ptr(), b)
         return self
 
     def kernel_families(self) -> List[str]:
-        fams = {"elementwise", "gemm_plain", "sampling", "gemv"}
+        fams = {"elementwise", "gemm_plain", "sampling", "gemv", "gemm_tc"}
         for layer in self.layers:
             fams.update(layer.kernel_families())
         return sorted(fams)
@@ -136,7 +130,6 @@ class Model:
 
     # ---------------------------------------------------------------- one step
     def forward(self, ctx: StepContext, cache, page_tables: List[torch.Tensor]) -> torch.Tensor:
-        ctx.extras["weight_after"] = self.weight_after
         resid = torch.empty((ctx.n_tokens, self.spec.hidden), dtype=torch.float32, device=self.device)
         ops.embedding(self.embedding, ctx.tokens, resid)
         stream = ResidualStream(resid)

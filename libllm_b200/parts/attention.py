@@ -10,7 +10,7 @@ from ..csrc import ops
 from ..errors import ConfigError, UnsupportedError
 from ..weights.state_map import TensorNeed
 from . import fast
-from .base import CacheNeed, LayerCache, Mixer, StepContext, next_weight
+from .base import CacheNeed, LayerCache, Mixer, StepContext
 from .linear import linear
 from .registry import build_part, part
 
@@ -56,10 +56,7 @@ class Attention(Mixer):
             self.b_qkv = torch.cat([fetch(n).to(torch.float32) for n in needs[4:7]]).contiguous()
 
     def kernel_families(self) -> List[str]:
-        return ["rope", "attention_generic", "gemm_plain", "gemv", "attention_decode", "attention_prefill"]
-
-    def streamed_weights(self) -> List[torch.Tensor]:
-        return [self.w_qkv, self.w_o]
+        return ["rope", "attention_generic", "gemm_plain", "gemv", "gemm_tc", "attention_decode", "attention_decode_tc", "attention_prefill"]
 
     def cache_need(self) -> Optional[CacheNeed]:
         s = self.spec
@@ -70,9 +67,14 @@ class Attention(Mixer):
         s = self.spec
         # The products hand over 32-bit results: q and k are rounded to the engine's
         # type once, after the rotation, and the residual addition gets an unrounded term.
-        qkv = linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32, prefetch=next_weight(ctx, self.w_qkv))
+        qkv = linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
         if self.position is None:
             raise UnsupportedError("attention without a position encoding is not built")
+        table = getattr(self.position, "table", None)
+        if table is not None and self.b_qkv is None:
+            out = fast.fused_decode_attention(ctx, qkv, cache, s, table, self.scale)
+            if out is not None:
+                return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
         q = torch.empty((ctx.n_tokens, self.q_width), dtype=ctx.dtype, device=ctx.device)
         ops.rope_cache_write(qkv, q, s.n_heads, s.n_kv_heads, s.head_dim, self.position.table,
                              ctx.tok_seq, ctx.tok_pos, cache.page_table, cache.k, cache.v,
@@ -82,4 +84,4 @@ class Attention(Mixer):
             out = torch.empty((ctx.n_tokens, self.q_width), dtype=ctx.dtype, device=ctx.device)
             ops.attention_generic(q, out, cache.k, cache.v, ctx.tok_seq, ctx.tok_pos, cache.page_table,
                                   s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size, s.window, self.scale)
-        return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True, prefetch=next_weight(ctx, self.w_o))
+        return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)

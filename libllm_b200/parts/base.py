@@ -83,12 +83,6 @@ class StepContext:
     extras: Dict[str, Any] = field(default_factory=dict)
 
 
-def next_weight(ctx: "StepContext", w: torch.Tensor) -> Optional[torch.Tensor]:
-    """The matrix that the step multiplies by after ``w``, if the model knows it."""
-    chain = ctx.extras.get("weight_after")
-    return chain.get(w.data_ptr()) if chain else None
-
-
 class ResidualStream:
     """The 32-bit residual stream and an addition that has not been applied yet.  The
     addition is folded into the next norm's pass over the row."""
@@ -113,13 +107,6 @@ class Part:
 
     def kernel_families(self) -> List[str]:
         """Kernel families (libllm_b200/csrc/build.py) this part launches."""
-        return []
-
-    def streamed_weights(self) -> List[torch.Tensor]:
-        """The matrices this part multiplies by, in the order it uses them.  The model chains
-        those of all parts in the order layers run, and a product may ask for the matrix
-        after its own to be brought into L2 (``next_weight``).  A part that names none
-        just gets no such help."""
         return []
 
 

@@ -37,9 +37,6 @@ class PreNormBlock(Block):
     def kernel_families(self) -> List[str]:
         return sorted({f for p in self.parts() for f in p.kernel_families()})
 
-    def streamed_weights(self):
-        return [w for p in self.parts() for w in p.streamed_weights()]
-
     def forward(self, ctx: StepContext, stream: ResidualStream, cache: Optional[LayerCache],
                 state: Optional[Dict[str, torch.Tensor]]) -> None:
         h = self.mixer_norm.forward(ctx, stream)

@@ -14,7 +14,11 @@ ENABLED = {
     "gemv": os.environ.get("LIBLLM_B200_NO_GEMV") is None,
     "decode_attention": os.environ.get("LIBLLM_B200_NO_DECODE_ATTENTION") is None,
     "prefill_attention": os.environ.get("LIBLLM_B200_NO_PREFILL_ATTENTION") is None,
+    "gemm_tc": os.environ.get("LIBLLM_B200_NO_GEMM_TC") is None,
+    "decode_attention_tc": os.environ.get("LIBLLM_B200_NO_DECODE_ATTENTION_TC") is None,
 }
+PRODUCT = os.environ.get("LIBLLM_B200_PRODUCT", "tc")           # "gemv": never the tcgen05 kernel
+TC_TOKENS = int(os.environ.get("LIBLLM_B200_TC_TOKENS", "256"))
 SM_COUNT = 148
 # Above this many tokens the library product is faster than the weight streamer (measured at the
 # layer sizes of Llama-3.2-1B: 181 us against 661 us for a layer's products at 64 tokens).
@@ -22,20 +26,29 @@ GEMV_TOKENS = int(os.environ.get("LIBLLM_B200_GEMV_TOKENS", "16"))
 
 
 def small_batch_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
-                       parts_ok: bool = False, prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-    """The weight-streaming product for steps of up to 64 tokens.  With ``parts_ok`` the
-    result may come as [parts, T, N] partial products over K (32-bit) that the caller adds:
-    matrices with few rows are cut along K so that every SM has work."""
-    if not ENABLED["gemv"] or x.shape[0] > GEMV_TOKENS or not ops.gemv_supported(x, w):
-        return None
+                       parts_ok: bool = False) -> Optional[torch.Tensor]:
+    """The product for steps of few tokens, where reading the weights once is what costs: the
+    mma.sync weight streamer up to ``GEMV_TOKENS`` tokens, the tcgen05 kernel up to ``TC_TOKENS``.  With ``parts_ok`` the result may come
+    as [parts, T, N] partial products over K (32-bit) that the caller adds: matrices with few
+    rows are cut along K so that every SM has work."""
+    T = x.shape[0]
     n = w.shape[0] // 2 if swiglu else w.shape[0]
+    use_gemv = ENABLED["gemv"] and T <= GEMV_TOKENS and ops.gemv_supported(x, w)
+    if PRODUCT == "tc" and ENABLED["gemm_tc"] and T <= TC_TOKENS and not use_gemv and ops.gemm_tc_supported(x, w):
+        if parts_ok and not swiglu and out_dtype == torch.float32:
+            parts = ops.gemm_tc_suggest_parts(T, n, x.shape[1])
+            if parts > 1:
+                return ops.gemm_tc(x, w, torch.empty((parts, T, n), dtype=out_dtype, device=x.device))
+        return ops.gemm_tc(x, w, torch.empty((T, n), dtype=out_dtype, device=x.device), swiglu)
+    if not use_gemv:
+        return None
     if parts_ok and not swiglu and out_dtype == torch.float32:
-        parts = ops.gemv_suggest_parts(x.shape[0], n, x.shape[1])
+        parts = ops.gemv_suggest_parts(T, n, x.shape[1])
         if parts > 1:
-            out = torch.empty((parts, x.shape[0], n), dtype=out_dtype, device=x.device)
-            return ops.gemv_bf16(x, w, out, prefetch=prefetch)
-    out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
-    return ops.gemv_bf16(x, w, out, swiglu, prefetch=prefetch)
+            out = torch.empty((parts, T, n), dtype=out_dtype, device=x.device)
+            return ops.gemv_bf16(x, w, out)
+    out = torch.empty((T, n), dtype=out_dtype, device=x.device)
+    return ops.gemv_bf16(x, w, out, swiglu)
 
 
 def decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int) -> Tuple[int, int]:
@@ -50,6 +63,39 @@ def decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int) -> Tup
     chunk = (chunk + page_size - 1) // page_size * page_size
     n_splits = (max_kv_len + chunk - 1) // chunk
     return chunk, max(1, n_splits)
+
+
+_counters = {}
+
+
+def _zero_counters(device, n: int) -> torch.Tensor:
+    """int32 zeros that the fused decode attention counts finished splits in (and leaves zero)."""
+    t = _counters.get(device)
+    if t is None or t.numel() < n:
+        t = _counters[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return t
+
+
+def fused_decode_attention(ctx, qkv: torch.Tensor, cache, spec, table: torch.Tensor,
+                           scale: float) -> Optional[torch.Tensor]:
+    """Rotation, cache append and attention of a decode-only step in one launch; None when the
+    kernel does not take the case (then the parts run one after another)."""
+    group = spec.n_heads // spec.n_kv_heads
+    if not (ctx.decode_only and ENABLED["decode_attention_tc"] and ctx.dtype == torch.bfloat16
+            and qkv.dtype == torch.float32 and qkv.dim() == 2
+            and ops.attention_decode_tc_supported(spec.head_dim, cache.page_size, group)):
+        return None
+    chunk, n_splits = decode_split(ctx.n_seqs, spec.n_kv_heads, max(ctx.max_kv_len, 1), cache.page_size)
+    dev = qkv.device
+    out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=torch.bfloat16, device=dev)
+    ws_o = ws_ml = counters = None
+    if n_splits > 1:
+        ws_o = torch.empty(ctx.n_seqs * spec.n_heads * n_splits * spec.head_dim, dtype=torch.float32, device=dev)
+        ws_ml = torch.empty(ctx.n_seqs * spec.n_heads * n_splits * 2, dtype=torch.float32, device=dev)
+        counters = _zero_counters(dev, ctx.n_seqs * spec.n_kv_heads)
+    return ops.attention_decode_tc(qkv, out, table, cache.k, cache.v, ctx.tok_pos, cache.page_table, spec.n_heads,
+                                   spec.n_kv_heads, spec.head_dim, cache.page_size, chunk, n_splits, spec.window,
+                                   scale, cache.writes, ws_o, ws_ml, counters)
 
 
 def attention(ctx, q: torch.Tensor, cache, spec, scale: float) -> Optional[torch.Tensor]:

@@ -34,12 +34,10 @@ def _library_mm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None, parts_ok: bool = False,
-           prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, parts_ok: bool = False) -> torch.Tensor:
     """x [T, K] in the engine's type, w [N, K]; returns [T, N] in ``out_dtype``.  With
     ``parts_ok`` (for results that go into the residual addition, which adds parts in
-    order) the result may be [parts, T, N] partial products to be summed.  ``prefetch`` is
-    the matrix the step multiplies by next (a hint: see ``next_weight``)."""
+    order) the result may be [parts, T, N] partial products to be summed."""
     if not x.is_cuda:
         raise ExtensionError("linear: activations must be on a CUDA device (there is no CPU fallback)")
     out_dtype = out_dtype or x.dtype
@@ -48,7 +46,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         out = torch.empty((T, w.shape[0]), dtype=out_dtype, device=x.device)
         return ops.gemm_plain(x, w, out, bias)
     from . import fast
-    y = fast.small_batch_linear(x, w, out_dtype, parts_ok=parts_ok, prefetch=prefetch)
+    y = fast.small_batch_linear(x, w, out_dtype, parts_ok=parts_ok)
     if y is not None:
         return y
     return _library_mm(x, w, out_dtype)

@@ -8,7 +8,7 @@ import torch
 from ..csrc import ops
 from ..weights.state_map import TensorNeed
 from . import fast
-from .base import FeedForward, StepContext, next_weight
+from .base import FeedForward, StepContext
 from .linear import linear
 from .registry import part
 
@@ -30,17 +30,12 @@ class SwiGLU(FeedForward):
         self.w_down = fetch(needs[2])
 
     def kernel_families(self) -> List[str]:
-        return ["elementwise", "gemm_plain", "gemv"]
-
-    def streamed_weights(self) -> List[torch.Tensor]:
-        return [self.w_gate_up, self.w_down]
+        return ["elementwise", "gemm_plain", "gemv", "gemm_tc"]
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
-        after_down = next_weight(ctx, self.w_down)
-        m = fast.small_batch_linear(x, self.w_gate_up, ctx.dtype, swiglu=True, prefetch=self.w_down) \
-            if x.dtype == torch.bfloat16 else None
+        m = fast.small_batch_linear(x, self.w_gate_up, ctx.dtype, swiglu=True) if x.dtype == torch.bfloat16 else None
         if m is not None:
-            return linear(m, self.w_down, out_dtype=torch.float32, parts_ok=True, prefetch=after_down)
+            return linear(m, self.w_down, out_dtype=torch.float32, parts_ok=True)
         gu = linear(x, self.w_gate_up, out_dtype=torch.float32)
         m = torch.empty((x.shape[0], self.spec.intermediate), dtype=ctx.dtype, device=ctx.device)
         ops.swiglu(gu, m)

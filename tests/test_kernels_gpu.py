@@ -460,3 +460,48 @@ def test_tensor_core_product_rows_do_not_depend_on_the_batch():
         ops.gemm_tc(x[r:r + 1].contiguous(), w, one)
         assert torch.equal(one[0], full[r])
     ops.check_tc_status()
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d,window", [(4, 2, 16, None), (3, 1, 32, None), (32, 8, 64, None), (8, 1, 128, None),
+                                                     (8, 8, 64, None), (6, 2, 128, 100), (10, 2, 48, None)])
+@pytest.mark.parametrize("chunk,n_splits", [(64, 16), (192, 6), (1024, 1)])
+def test_attention_decode_fused(n_heads, n_kv, d, window, chunk, n_splits):
+    """Rotation, cache append, attention and the joining of splits in one launch: the outputs
+    against the plain rotation + attention, the cache rows it must have written, and a second
+    launch one position later (the counters must have come back to zero)."""
+    from libllm_b200.csrc import ops
+    from libllm_b200.parts.rope import rotary_frequencies
+    page = 64
+    lens = [1, 70, 333, 1000, 64, 65]        # cached tokens, the new one included
+    B = len(lens)
+    K, V, table_pt, ks, vs = paged_cache(B, [l + 1 for l in lens], n_kv, d, page, "bfloat16", 60)
+    freqs = torch.tensor(rotary_frequencies(d, 10000.0, None), dtype=torch.float64)
+    ang = torch.arange(1100, dtype=torch.float64)[:, None] * freqs[None]
+    table = torch.cat([ang.cos(), ang.sin()], 1).float().to(DEV)
+    counters = torch.zeros(B * n_kv, dtype=torch.int32, device=DEV)
+    for step in range(2):
+        pos = [l - 1 + step for l in lens]
+        qkv = (torch.randn((B, (n_heads + 2 * n_kv) * d), generator=torch.Generator().manual_seed(61 + step))).to(DEV)
+        out = torch.full((B, n_heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ws_o = torch.full((B * n_heads * n_splits * d,), float("nan"), device=DEV)
+        ws_ml = torch.full((B * n_heads * n_splits * 2,), float("nan"), device=DEV)
+        tok_pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
+        assert ops.attention_decode_tc_supported(d, page, n_heads // n_kv)
+        ops.attention_decode_tc(qkv, out, table, K, V, tok_pos, table_pt, n_heads, n_kv, d, page, chunk, n_splits, window,
+                                1 / math.sqrt(d), True, ws_o, ws_ml, counters)
+        assert int(counters.abs().sum()) == 0
+        x = qkv.cpu().view(B, n_heads + 2 * n_kv, d)
+        for b in range(B):
+            p = torch.tensor([pos[b]], dtype=torch.float64)
+            q = P.rope_rotate(x[b:b + 1, :n_heads], p, freqs).to(torch.bfloat16)
+            k_new = P.rope_rotate(x[b:b + 1, n_heads:n_heads + n_kv], p, freqs).to(torch.bfloat16)
+            v_new = x[b:b + 1, n_heads + n_kv:].to(torch.bfloat16)
+            # the plain side's cache: the rows before the new token as they were, then the new one
+            ks[b][pos[b]] = k_new[0]
+            vs[b][pos[b]] = v_new[0]
+            pg = int(table_pt[b, pos[b] // page])
+            assert torch.equal(K[pg, :, pos[b] % page].cpu(), k_new[0]) or \
+                float((K[pg, :, pos[b] % page].cpu().float() - k_new[0].float()).abs().max()) <= 2 ** -7 * float(k_new.abs().max())
+            assert torch.equal(V[pg, :, pos[b] % page].cpu(), v_new[0])
+            ref = P.attention_scores_softmax_values(q, ks[b][:pos[b] + 1], vs[b][:pos[b] + 1], window)
+            close(out[b].view(1, n_heads, d), ref, "bfloat16", scale=1.0)
