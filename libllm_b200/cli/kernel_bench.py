@@ -142,20 +142,38 @@ def bench_attention_decode(args, timer):
     from ..parts import fast
     B, ctx, nH, nKV, d = args.batch, args.context, args.heads, args.kv_heads, args.head_dim
     k, v, table = _paged_cache(B, ctx, nKV, d)
-    q = torch.randn(B, nH * d, device="cuda").to(torch.bfloat16)
-    out = torch.empty_like(q)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
-    chunk, n_splits = fast.decode_split(B, nKV, table.shape[1] * 64, 64)
-    ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
-    ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    nbytes = 2 * B * ctx * nKV * d * 2 + 2 * B * nH * d * 2
+    if args.separate:
+        q = torch.randn(B, nH * d, device="cuda").to(torch.bfloat16)
+        out = torch.empty_like(q)
+        chunk, n_splits = fast.decode_split(B, nKV, table.shape[1] * 64, 64)
+        ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
+        ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
 
-    def fn():
-        ops.attention_decode(q, out, k, v, pos, table, nH, nKV, d, 64, chunk, n_splits, None, 1.0 / math.sqrt(d),
-                             ws_o if n_splits > 1 else None, ws_ml if n_splits > 1 else None)
+        def fn():
+            ops.attention_decode(q, out, k, v, pos, table, nH, nKV, d, 64, chunk, n_splits, None, scale,
+                                 ws_o if n_splits > 1 else None, ws_ml if n_splits > 1 else None)
+        name = "attention_decode (FMA kernel + join kernel)"
+    else:
+        qkv = torch.randn(B, (nH + 2 * nKV) * d, device="cuda")
+        out = torch.empty(B, nH * d, device="cuda", dtype=torch.bfloat16)
+        ang = torch.arange(ctx + 1, device="cuda", dtype=torch.float64)[:, None] * \
+            (10000.0 ** (-torch.arange(0, d, 2, device="cuda", dtype=torch.float64) / d))[None]
+        rope = torch.cat([ang.cos(), ang.sin()], 1).float().contiguous()
+        chunk, n_splits = fast.fused_decode_split(B, nKV, table.shape[1] * 64, 64)
+        ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
+        ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
+        counters = torch.zeros(B * nKV, dtype=torch.int32, device="cuda")
+
+        def fn():
+            ops.attention_decode_tc(qkv, out, rope, k, v, pos, table, nH, nKV, d, 64, chunk, n_splits, None, scale,
+                                    True, ws_o, ws_ml, counters)
+        name = "attention_decode_tc (rotation, append, attention, join)"
     us = timer.run(fn)
-    report("attention_decode", us, bytes_moved=2 * B * ctx * nKV * d * 2 + 2 * B * nH * d * 2,
-           flops=4 * B * nH * ctx * d, batch=B, context=ctx, heads=nH, kv_heads=nKV, head_dim=d,
-           chunk=chunk, splits=n_splits)
+    report(name, us, bytes_moved=nbytes, flops=4 * B * nH * ctx * d, batch=B, context=ctx, heads=nH, kv_heads=nKV,
+           head_dim=d, chunk=chunk, splits=n_splits)
 
 
 def bench_attention_prefill(args, timer):
@@ -242,6 +260,8 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--tc", action="store_true", help="gemv, layer_products: time the tcgen05 product")
     ap.add_argument("--library", action="store_true", help="gemv, layer_products: time the library product instead")
+    ap.add_argument("--separate", action="store_true",
+                    help="attention_decode: time the FMA kernel with its join kernel instead of the fused one")
     ap.add_argument("--generic", action="store_true", help="attention_prefill: time the general kernel")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

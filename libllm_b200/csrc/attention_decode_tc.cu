@@ -7,7 +7,8 @@
 // products and the issue slots stay free for the loads, which is what this kernel is bound
 // by (it reads K and V once; a kernel that computes the scores on the FMA pipe spends its
 // time issuing).  Key tiles are pages of the cache ([64, d] contiguous) fetched by 16-byte
-// asynchronous copies, two in flight; each of the four warps takes 16 keys of a tile with a
+// asynchronous copies, two to four in flight (issued before the dependency on the previous kernel is
+// waited for); each of the four warps takes 16 keys of a tile with a
 // running maximum and sum of its own, and the four are joined at the end.
 //
 // What the reference does in some twenty launches per layer (fourteen for the rotation,
@@ -30,9 +31,13 @@ constexpr int DT_WARPS = 4;
 constexpr int DT_BN = 64;      // keys per tile = tokens per page
 constexpr int DT_ROWS = 16;    // rows of the MMA tile: query heads of one group
 
+// Key/value tiles kept in flight per CTA: about 75 KB of shared memory whatever the head size.
+__host__ __device__ constexpr int decode_tc_stages(int d) { return d <= 64 ? 4 : (d <= 96 ? 3 : 2); }
+
 template <int D>
 __global__ void __launch_bounds__(DT_WARPS * 32)
-attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, const float *__restrict__ table,
+attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, int qkv_parts,
+                           long long qkv_part_stride, const float *__restrict__ table,
                            int table_rows, int rot_dim, const int *__restrict__ tok_pos,
                            const int *__restrict__ page_table, int pt_stride, __nv_bfloat16 *__restrict__ kc,
                            __nv_bfloat16 *__restrict__ vc, int write_cache, int n_heads, int n_kv, int G, int chunk,
@@ -43,12 +48,13 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   constexpr int CHUNKS = D / 8;
   constexpr int KS = D / 16;
   constexpr int DT = D / 8;
+  constexpr int NS = decode_tc_stages(D);                    // key tiles in flight
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16 *sQ = reinterpret_cast<__nv_bfloat16 *>(smem_raw);           // [16][LD]
   __nv_bfloat16 *sNew = sQ + DT_ROWS * LD;                                    // [2][LD]: new k, new v
-  __nv_bfloat16 *sK = sNew + 2 * LD;                                          // [2][64][LD]
-  __nv_bfloat16 *sV = sK + 2 * DT_BN * LD;                                    // [2][64][LD]
-  int *s_pages = reinterpret_cast<int *>(sV + 2 * DT_BN * LD);
+  __nv_bfloat16 *sK = sNew + 2 * LD;                                          // [NS][64][LD]
+  __nv_bfloat16 *sV = sK + NS * DT_BN * LD;                                   // [NS][64][LD]
+  int *s_pages = reinterpret_cast<int *>(sV + NS * DT_BN * LD);
   __shared__ float sm_m[DT_WARPS][DT_ROWS], sm_l[DT_WARPS][DT_ROWS];
   __shared__ int s_last;
 
@@ -73,7 +79,6 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   const bool owns_new = write_cache && pos >= c0 && pos < c1;     // c1 = len here
   const int half = rot_dim / 2;
   const float *cs = table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim;
-  grid_dependency_wait();
   __syncthreads();
 
   auto load_kv = [&](int kt, int stage) {
@@ -86,19 +91,33 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
       cp_async16(dv + r * LD + ch * 8, vc + base + (size_t)r * D + ch * 8, true);
     }
   };
-  load_kv(first_tile, 0);
-  cp_async_commit();
+  // The cached keys and values of earlier tokens do not depend on the kernel before this one
+  // (positions and page tables come from the step's descriptor, copied before the step's first
+  // kernel): the first NS tiles are on their way while that kernel, the q|k|v product, still
+  // runs.  The new token's row is put into its tile by hand further down.
+#pragma unroll
+  for (int i = 0; i < NS; ++i) {
+    if (first_tile + i <= last_tile) load_kv(first_tile + i, i);
+    cp_async_commit();
+  }
+  grid_dependency_wait();
 
   // The group's queries, rotated, as rows of the MMA tile; rows beyond the group are zeros.
   const float *row = qkv + (size_t)b * qkv_stride;
+  // one value of the stacked row: the product's parts over K added in order
+  auto val = [&](const float *p) {
+    float v = p[0];
+    for (int i = 1; i < qkv_parts; ++i) v += p[(size_t)i * qkv_part_stride];
+    return v;
+  };
   for (int i = tid; i < DT_ROWS * D; i += DT_WARPS * 32) {
     const int h = i / D, c = i % D;
     float v = 0.f;
     if (h < G) {
       const float *qh = row + (size_t)(kvh * G + h) * D;
-      if (c < half) v = qh[c] * cs[c] - qh[c + half] * cs[half + c];
-      else if (c < rot_dim) v = qh[c] * cs[c - half] + qh[c - half] * cs[c];
-      else v = qh[c];
+      if (c < half) v = val(qh + c) * cs[c] - val(qh + c + half) * cs[half + c];
+      else if (c < rot_dim) v = val(qh + c) * cs[c - half] + val(qh + c - half) * cs[c];
+      else v = val(qh + c);
     }
     sQ[h * LD + c] = __float2bfloat16_rn(v);
   }
@@ -109,10 +128,10 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
     const size_t dst = (((size_t)page * n_kv + kvh) * DT_BN + (pos % DT_BN)) * D;
     for (int c = tid; c < D; c += DT_WARPS * 32) {
       float kv;
-      if (c < half) kv = kh[c] * cs[c] - kh[c + half] * cs[half + c];
-      else if (c < rot_dim) kv = kh[c] * cs[c - half] + kh[c - half] * cs[c];
-      else kv = kh[c];
-      const __nv_bfloat16 kb = __float2bfloat16_rn(kv), vb = __float2bfloat16_rn(vh[c]);
+      if (c < half) kv = val(kh + c) * cs[c] - val(kh + c + half) * cs[half + c];
+      else if (c < rot_dim) kv = val(kh + c) * cs[c - half] + val(kh + c - half) * cs[c];
+      else kv = val(kh + c);
+      const __nv_bfloat16 kb = __float2bfloat16_rn(kv), vb = __float2bfloat16_rn(val(vh + c));
       sNew[c] = kb;
       sNew[LD + c] = vb;
       kc[dst + c] = kb;
@@ -128,11 +147,10 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
+  __syncthreads();                       // sQ and sNew are written
   for (int kt = first_tile; kt <= last_tile; ++kt) {
-    const int stage = (kt - first_tile) & 1;
-    if (kt + 1 <= last_tile) load_kv(kt + 1, stage ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();
+    const int stage = (kt - first_tile) % NS;
+    cp_async_wait<NS - 1>();             // one group per tile, NS - 1 newer ones may be in flight
     __syncthreads();
     __nv_bfloat16 *tk = sK + stage * DT_BN * LD, *tv = sV + stage * DT_BN * LD;
     if (owns_new && kt == pos / DT_BN) {
@@ -217,9 +235,12 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
         mma16816(o[2 * d2 + 1], pa, vb[2], vb[3]);
       }
     }
-    __syncthreads();
+    __syncthreads();                     // every warp is done with the stage
+    if (kt + NS <= last_tile) load_kv(kt + NS, stage);
+    cp_async_commit();
   }
   cp_async_wait<0>();
+  __syncthreads();
 
   // Join the four warps (each saw other keys): through shared memory, in warp order.
 #pragma unroll
@@ -303,13 +324,14 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
 }
 
 template <int D>
-static int launch_decode_tc(const float *qkv, long long qkv_stride, const float *table, int table_rows, int rot_dim,
+static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_parts, long long qkv_part_stride,
+                            const float *table, int table_rows, int rot_dim,
                             const int *tok_pos, const int *page_table, int pt_stride, void *kc, void *vc,
                             int write_cache, int n_seqs, int n_heads, int n_kv, int chunk, int n_splits, int window,
                             float scale, float *ws_o, float *ws_ml, int *counters, void *out, long long out_stride,
                             cudaStream_t stream) {
   constexpr int LD = D + 8;
-  const size_t tiles = (size_t)(DT_ROWS + 2 + 4 * DT_BN) * LD * sizeof(__nv_bfloat16);
+  const size_t tiles = (size_t)(DT_ROWS + 2 + 2 * decode_tc_stages(D) * DT_BN) * LD * sizeof(__nv_bfloat16);
   const size_t smem = tiles + (size_t)(chunk / DT_BN + 2) * sizeof(int);
   LLM_REQUIRE(smem <= 200 * 1024, "attention_decode_tc: a chunk of %d keys spans too many pages", chunk);
   auto kern = attention_decode_tc_kernel<D>;
@@ -317,7 +339,8 @@ static int launch_decode_tc(const float *qkv, long long qkv_stride, const float 
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    "attention_decode_tc attribute");
   dim3 grid(n_splits, n_kv, n_seqs);
-  LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(DT_WARPS * 32), smem, stream, qkv, qkv_stride, table, table_rows, rot_dim,
+  LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(DT_WARPS * 32), smem, stream, qkv, qkv_stride, qkv_parts, qkv_part_stride, table, table_rows,
+                            rot_dim,
                             tok_pos, page_table, pt_stride, (__nv_bfloat16 *)kc, (__nv_bfloat16 *)vc, write_cache,
                             n_heads, n_kv, n_heads / n_kv, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml,
                             counters, n_splits, (__nv_bfloat16 *)out, out_stride),
@@ -330,12 +353,14 @@ LLM_EXPORT int llm_attention_decode_tc_supports(int d, int page_size, int group)
   return page_size == DT_BN && d >= 16 && d <= 128 && d % 16 == 0 && group >= 1 && group <= DT_ROWS;
 }
 
-// qkv [B, (heads + 2 kv_heads) * d] 32-bit (the stacked product, not rotated), table
+// qkv [B, (heads + 2 kv_heads) * d] 32-bit (the stacked product, not rotated; with qkv_parts > 1 it
+// is the sum of that many partial products qkv_part_stride floats apart), table
 // [positions, rot_dim] (cosines, then sines), caches [pages, kv_heads, 64, d] bfloat16, tok_pos[b]
 // the position of sequence b's token.  With write_cache the token's k and v are appended.
 // ws_o needs B*heads*n_splits*d floats, ws_ml B*heads*n_splits*2, counters B*kv_heads ints that are
 // zero before the first launch (the kernel leaves them zero).
-LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, const float *table, int table_rows,
+LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, int qkv_parts,
+                                       long long qkv_part_stride, const float *table, int table_rows,
                                        int rot_dim, const int *tok_pos, const int *page_table, int pt_stride,
                                        void *kc, void *vc, int write_cache, int n_seqs, int n_heads, int n_kv, int d,
                                        int page_size, int chunk, int n_splits, int window, float scale, float *ws_o,
@@ -351,11 +376,12 @@ LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, c
               "attention_decode_tc: chunk %d must be a positive multiple of the page size", chunk);
   LLM_REQUIRE(rot_dim > 0 && rot_dim % 2 == 0 && rot_dim <= d, "attention_decode_tc: rotated width %d does not fit head size %d", rot_dim, d);
   LLM_REQUIRE(n_splits == 1 || (ws_o && ws_ml && counters), "attention_decode_tc: splits need scratch memory");
+  LLM_REQUIRE(qkv_parts >= 1 && qkv_parts <= 64, "attention_decode_tc: %d parts of the stacked product", qkv_parts);
   LLM_REQUIRE((uintptr_t)kc % 16 == 0 && (uintptr_t)vc % 16 == 0 && (uintptr_t)out % 4 == 0 && out_stride % 2 == 0,
               "attention_decode_tc: caches must be 16-byte aligned");
 #define DT_CASE(DD)                                                                                                 \
   if (d == DD)                                                                                                      \
-    return launch_decode_tc<DD>(qkv, qkv_stride, table, table_rows, rot_dim, tok_pos, page_table, pt_stride, kc, vc, \
+    return launch_decode_tc<DD>(qkv, qkv_stride, qkv_parts, qkv_part_stride, table, table_rows, rot_dim, tok_pos, page_table, pt_stride, kc, vc, \
                                 write_cache, n_seqs, n_heads, n_kv, chunk, n_splits, window, scale, ws_o, ws_ml,    \
                                 counters, out, out_stride, stream);
   DT_CASE(16) DT_CASE(32) DT_CASE(48) DT_CASE(64) DT_CASE(80) DT_CASE(96) DT_CASE(112) DT_CASE(128)

@@ -72,9 +72,22 @@ static inline bool llm_pdl_enabled() {
   return on;
 }
 
+// Every kernel of a step asks for the same split of an SM's on-chip memory (all of it as shared
+// memory): kernels that overlap under programmatic dependent launch then never make an SM wait
+// until it is empty to change the split.
+template <typename... KArgs>
+static inline void llm_same_carveout(void (*kernel)(KArgs...)) {
+  static thread_local const void *last = nullptr;
+  if (last == (const void *)kernel) return;
+  last = (const void *)kernel;
+  static const bool on = getenv("LIBLLM_B200_NO_CARVEOUT") == nullptr;
+  if (on) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t llm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                      cudaStream_t stream, Args... args) {
+  llm_same_carveout(kernel);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

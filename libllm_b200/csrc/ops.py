@@ -379,9 +379,15 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
     ``counters`` (int32, one per sequence and kv head) must be zero before the first launch; the
     kernel leaves it zero."""
     _on_gpu(qkv, out, table, kcache, vcache, tok_pos, page_table, ws_o, ws_ml, counters)
-    B = qkv.shape[0]
-    assert qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1
-    assert qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+    parts, part_stride = 1, 0
+    if qkv.dim() == 3:                       # [parts, B, W]: partial products over K, added in the kernel
+        parts, part_stride = qkv.shape[0], qkv.stride(0)
+        qkv2 = qkv[0]
+    else:
+        qkv2 = qkv
+    B = qkv2.shape[0]
+    assert qkv.dtype == torch.float32 and qkv2.dim() == 2 and qkv2.stride(1) == 1
+    assert qkv2.shape[1] == (n_heads + 2 * n_kv) * head_dim
     assert kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.stride(1) == 1
     assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     assert table.dtype == torch.float32 and table.is_contiguous() and table.dim() == 2
@@ -391,10 +397,11 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
         assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
         assert counters.dtype == torch.int32 and counters.numel() >= B * n_kv
     _call("attention_decode_tc", "llm_attention_decode_tc",
-          [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
-           c_longlong, c_void_p],
-          _ptr(qkv), qkv.stride(0) if B > 1 else qkv.shape[1], _ptr(table), table.shape[0], table.shape[1],
+          [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_longlong, c_void_p],
+          _ptr(qkv), qkv2.stride(0) if B > 1 else qkv2.shape[1], parts, part_stride, _ptr(table), table.shape[0],
+          table.shape[1],
           _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache), 1 if write_cache else 0,
           B, n_heads, n_kv, head_dim, page_size, chunk, n_splits, int(window or 0), float(scale), _ptr(ws_o),
           _ptr(ws_ml), _ptr(counters), _ptr(out), out.stride(0) if B > 1 else out.shape[1], _stream())

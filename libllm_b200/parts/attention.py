@@ -67,14 +67,16 @@ class Attention(Mixer):
         s = self.spec
         # The products hand over 32-bit results: q and k are rounded to the engine's
         # type once, after the rotation, and the residual addition gets an unrounded term.
-        qkv = linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32)
+        table = getattr(self.position, "table", None) if self.position is not None else None
+        fused = table is not None and self.b_qkv is None and fast.fused_decode_possible(ctx, cache, s)
+        qkv = linear(x, self.w_qkv, self.b_qkv, out_dtype=torch.float32, parts_ok=fused)
         if self.position is None:
             raise UnsupportedError("attention without a position encoding is not built")
-        table = getattr(self.position, "table", None)
-        if table is not None and self.b_qkv is None:
+        if fused:
             out = fast.fused_decode_attention(ctx, qkv, cache, s, table, self.scale)
             if out is not None:
                 return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
+            raise UnsupportedError("attention: the fused decode kernel refused a step it had accepted")
         q = torch.empty((ctx.n_tokens, self.q_width), dtype=ctx.dtype, device=ctx.device)
         ops.rope_cache_write(qkv, q, s.n_heads, s.n_kv_heads, s.head_dim, self.position.table,
                              ctx.tok_seq, ctx.tok_pos, cache.page_table, cache.k, cache.v,

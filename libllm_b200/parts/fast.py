@@ -20,9 +20,11 @@ ENABLED = {
 PRODUCT = os.environ.get("LIBLLM_B200_PRODUCT", "tc")           # "gemv": never the tcgen05 kernel
 TC_TOKENS = int(os.environ.get("LIBLLM_B200_TC_TOKENS", "256"))
 SM_COUNT = 148
-# Above this many tokens the library product is faster than the weight streamer (measured at the
-# layer sizes of Llama-3.2-1B: 181 us against 661 us for a layer's products at 64 tokens).
-GEMV_TOKENS = int(os.environ.get("LIBLLM_B200_GEMV_TOKENS", "16"))
+# Steps of up to this many tokens take the mma.sync weight streamer (csrc/gemv.cu) instead of the
+# tcgen05 product.  Off by default: inside a step the two are equally fast at 8 tokens, but the
+# streamer reads its tokens through L1 and slows down when a kernel with much shared memory runs
+# beside it, and above 16 tokens it falls behind (661 us against 181 us for a layer's products at 64).
+GEMV_TOKENS = int(os.environ.get("LIBLLM_B200_GEMV_TOKENS", "0"))
 
 
 def small_batch_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
@@ -76,16 +78,33 @@ def _zero_counters(device, n: int) -> torch.Tensor:
     return t
 
 
+def fused_decode_possible(ctx, cache, spec) -> bool:
+    group = spec.n_heads // spec.n_kv_heads
+    return bool(ctx.decode_only and ENABLED["decode_attention_tc"] and ctx.dtype == torch.bfloat16 and cache is not None
+                and ops.attention_decode_tc_supported(spec.head_dim, cache.page_size, group))
+
+
+def fused_decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int) -> Tuple[int, int]:
+    """(chunk, n_splits) for the fused decode attention: about two and a half CTAs per SM (three fit),
+    each with at least a few pages so that its ring of tiles is worth filling; like ``decode_split``
+    it depends on the graph's bound on the length, not on the lengths themselves."""
+    pairs = max(1, n_seqs * n_kv)
+    want = max(1, (5 * SM_COUNT // 2 + pairs - 1) // pairs)
+    most = max(1, max_kv_len // page_size)
+    n_splits = max(1, min(want, most))
+    chunk = (max_kv_len + n_splits - 1) // n_splits
+    chunk = (chunk + page_size - 1) // page_size * page_size
+    return chunk, max(1, (max_kv_len + chunk - 1) // chunk)
+
+
 def fused_decode_attention(ctx, qkv: torch.Tensor, cache, spec, table: torch.Tensor,
                            scale: float) -> Optional[torch.Tensor]:
     """Rotation, cache append and attention of a decode-only step in one launch; None when the
-    kernel does not take the case (then the parts run one after another)."""
-    group = spec.n_heads // spec.n_kv_heads
-    if not (ctx.decode_only and ENABLED["decode_attention_tc"] and ctx.dtype == torch.bfloat16
-            and qkv.dtype == torch.float32 and qkv.dim() == 2
-            and ops.attention_decode_tc_supported(spec.head_dim, cache.page_size, group)):
+    kernel does not take the case (then the parts run one after another).  ``qkv`` is the 32-bit
+    stacked product, [T, W] or [parts, T, W]."""
+    if not fused_decode_possible(ctx, cache, spec) or qkv.dtype != torch.float32:
         return None
-    chunk, n_splits = decode_split(ctx.n_seqs, spec.n_kv_heads, max(ctx.max_kv_len, 1), cache.page_size)
+    chunk, n_splits = fused_decode_split(ctx.n_seqs, spec.n_kv_heads, max(ctx.max_kv_len, 1), cache.page_size)
     dev = qkv.device
     out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=torch.bfloat16, device=dev)
     ws_o = ws_ml = counters = None
