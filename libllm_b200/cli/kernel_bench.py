@@ -162,7 +162,7 @@ def bench_attention_decode(args, timer):
         ang = torch.arange(ctx + 1, device="cuda", dtype=torch.float64)[:, None] * \
             (10000.0 ** (-torch.arange(0, d, 2, device="cuda", dtype=torch.float64) / d))[None]
         rope = torch.cat([ang.cos(), ang.sin()], 1).float().contiguous()
-        chunk, n_splits = fast.fused_decode_split(B, nKV, table.shape[1] * 64, 64)
+        chunk, n_splits = fast.fused_decode_split(B, nKV, table.shape[1] * 64, 64, d)
         ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
         ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
         counters = torch.zeros(B * nKV, dtype=torch.int32, device="cuda")

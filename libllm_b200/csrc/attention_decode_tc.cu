@@ -31,11 +31,13 @@ constexpr int DT_WARPS = 4;
 constexpr int DT_BN = 64;      // keys per tile = tokens per page
 constexpr int DT_ROWS = 16;    // rows of the MMA tile: query heads of one group
 
-// Key/value tiles kept in flight per CTA: about 75 KB of shared memory whatever the head size.
-__host__ __device__ constexpr int decode_tc_stages(int d) { return d <= 64 ? 4 : (d <= 96 ? 3 : 2); }
+// Key/value tiles kept in flight per CTA.  Two, so that a CTA is small and several share an SM (five
+// at head size 64, three at 128): the loads in flight per SM come from the number of CTAs, and a
+// step's CTAs all fit on the GPU at once instead of running in one and a bit waves.
+__host__ __device__ constexpr int decode_tc_stages(int d) { return 2; }
 
 template <int D>
-__global__ void __launch_bounds__(DT_WARPS * 32)
+__global__ void __launch_bounds__(DT_WARPS * 32, D <= 64 ? 5 : 3)
 attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, int qkv_parts,
                            long long qkv_part_stride, const float *__restrict__ table,
                            int table_rows, int rot_dim, const int *__restrict__ tok_pos,
@@ -102,40 +104,94 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   }
   grid_dependency_wait();
 
-  // The group's queries, rotated, as rows of the MMA tile; rows beyond the group are zeros.
+  // The group's queries, rotated, as rows of the MMA tile (rows beyond the group are zeros), and
+  // the new token's key (rotated) and value: into the cache, and kept for this CTA's own tile.
   const float *row = qkv + (size_t)b * qkv_stride;
-  // one value of the stacked row: the product's parts over K added in order
-  auto val = [&](const float *p) {
-    float v = p[0];
-    for (int i = 1; i < qkv_parts; ++i) v += p[(size_t)i * qkv_part_stride];
-    return v;
-  };
-  for (int i = tid; i < DT_ROWS * D; i += DT_WARPS * 32) {
-    const int h = i / D, c = i % D;
-    float v = 0.f;
-    if (h < G) {
-      const float *qh = row + (size_t)(kvh * G + h) * D;
-      if (c < half) v = val(qh + c) * cs[c] - val(qh + c + half) * cs[half + c];
-      else if (c < rot_dim) v = val(qh + c) * cs[c - half] + val(qh + c - half) * cs[c];
-      else v = val(qh + c);
-    }
-    sQ[h * LD + c] = __float2bfloat16_rn(v);
-  }
-  // The new token's key (rotated) and value: into the cache, and kept for this CTA's own tile.
+  size_t new_dst = 0;
   if (owns_new) {
-    const float *kh = row + (size_t)(n_heads + kvh) * D, *vh = row + (size_t)(n_heads + n_kv + kvh) * D;
     const int page = s_pages[pos / DT_BN - first_tile];
-    const size_t dst = (((size_t)page * n_kv + kvh) * DT_BN + (pos % DT_BN)) * D;
-    for (int c = tid; c < D; c += DT_WARPS * 32) {
-      float kv;
-      if (c < half) kv = val(kh + c) * cs[c] - val(kh + c + half) * cs[half + c];
-      else if (c < rot_dim) kv = val(kh + c) * cs[c - half] + val(kh + c - half) * cs[c];
-      else kv = val(kh + c);
-      const __nv_bfloat16 kb = __float2bfloat16_rn(kv), vb = __float2bfloat16_rn(val(vh + c));
-      sNew[c] = kb;
-      sNew[LD + c] = vb;
-      kc[dst + c] = kb;
-      vc[dst + c] = vb;
+    new_dst = (((size_t)page * n_kv + kvh) * DT_BN + (pos % DT_BN)) * D;
+  }
+  constexpr int MAXP = 4;
+  const bool vec = rot_dim == D && qkv_parts <= MAXP && (qkv_stride % 4 == 0) && (qkv_part_stride % 4 == 0) &&
+                   ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)table % 16 == 0);
+  if (vec) {
+    // Four channel pairs per item; an item issues the loads of all parts before it adds them (in
+    // order), so the CTA waits for memory once.  Items: G heads of q, then k, then v (two halves).
+    constexpr int GROUPS = D / 8;                          // items per head
+    const int n_items = (G + (owns_new ? 2 : 0)) * GROUPS;
+    for (int i = tid; i < DT_ROWS * D / 8; i += DT_WARPS * 32)      // rows beyond the group
+      if (i / (D / 8) >= G) *reinterpret_cast<uint4 *>(sQ + (i / (D / 8)) * LD + (i % (D / 8)) * 8) = make_uint4(0, 0, 0, 0);
+    for (int item = tid; item < n_items; item += DT_WARPS * 32) {
+      const int h = item / GROUPS, j = (item % GROUPS) * 4;
+      const bool is_k = h == G, is_v = h == G + 1;
+      const float *src = row + (size_t)(is_v ? n_heads + n_kv + kvh : (is_k ? n_heads + kvh : kvh * G + h)) * D;
+      float4 a[MAXP], bb[MAXP];
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < qkv_parts) {
+          a[p] = ld4(src + (size_t)p * qkv_part_stride + j);
+          bb[p] = ld4(src + (size_t)p * qkv_part_stride + j + D / 2);
+        }
+      const float4 c = ld4(cs + j), sn = ld4(cs + D / 2 + j);
+      float4 x = a[0], y = bb[0];
+#pragma unroll
+      for (int p = 1; p < MAXP; ++p)
+        if (p < qkv_parts) {
+          x.x += a[p].x; x.y += a[p].y; x.z += a[p].z; x.w += a[p].w;
+          y.x += bb[p].x; y.y += bb[p].y; y.z += bb[p].z; y.w += bb[p].w;
+        }
+      float4 lo, hi;
+      if (is_v) {
+        lo = x;
+        hi = y;
+      } else {
+        lo = make_float4(x.x * c.x - y.x * sn.x, x.y * c.y - y.y * sn.y, x.z * c.z - y.z * sn.z, x.w * c.w - y.w * sn.w);
+        hi = make_float4(y.x * c.x + x.x * sn.x, y.y * c.y + x.y * sn.y, y.z * c.z + x.z * sn.z, y.w * c.w + x.w * sn.w);
+      }
+      if (h < G) {
+        st4(sQ + h * LD + j, lo);
+        st4(sQ + h * LD + j + D / 2, hi);
+      } else {
+        __nv_bfloat16 *keep = sNew + (is_v ? LD : 0);
+        st4(keep + j, lo);
+        st4(keep + j + D / 2, hi);
+        __nv_bfloat16 *dstc = (is_v ? vc : kc) + new_dst;
+        st4(dstc + j, lo);
+        st4(dstc + j + D / 2, hi);
+      }
+    }
+  } else {
+    // one value of the stacked row: the product's parts over K added in order
+    auto val = [&](const float *p) {
+      float v = p[0];
+      for (int i = 1; i < qkv_parts; ++i) v += p[(size_t)i * qkv_part_stride];
+      return v;
+    };
+    for (int i = tid; i < DT_ROWS * D; i += DT_WARPS * 32) {
+      const int h = i / D, c = i % D;
+      float v = 0.f;
+      if (h < G) {
+        const float *qh = row + (size_t)(kvh * G + h) * D;
+        if (c < half) v = val(qh + c) * cs[c] - val(qh + c + half) * cs[half + c];
+        else if (c < rot_dim) v = val(qh + c) * cs[c - half] + val(qh + c - half) * cs[c];
+        else v = val(qh + c);
+      }
+      sQ[h * LD + c] = __float2bfloat16_rn(v);
+    }
+    if (owns_new) {
+      const float *kh = row + (size_t)(n_heads + kvh) * D, *vh = row + (size_t)(n_heads + n_kv + kvh) * D;
+      for (int c = tid; c < D; c += DT_WARPS * 32) {
+        float kv;
+        if (c < half) kv = val(kh + c) * cs[c] - val(kh + c + half) * cs[half + c];
+        else if (c < rot_dim) kv = val(kh + c) * cs[c - half] + val(kh + c - half) * cs[c];
+        else kv = val(kh + c);
+        const __nv_bfloat16 kb = __float2bfloat16_rn(kv), vb = __float2bfloat16_rn(val(vh + c));
+        sNew[c] = kb;
+        sNew[LD + c] = vb;
+        kc[new_dst + c] = kb;
+        vc[new_dst + c] = vb;
+      }
     }
   }
 
@@ -346,6 +402,15 @@ static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_part
                             counters, n_splits, (__nv_bfloat16 *)out, out_stride),
                  "attention_decode_tc launch");
   return LLM_OK;
+}
+
+// CTAs of this kernel that fit one SM at head size d (shared memory and registers), for choosing
+// how many key splits fill the GPU once.
+LLM_EXPORT int llm_attention_decode_tc_ctas_per_sm(int d) {
+  const size_t smem = (size_t)(DT_ROWS + 2 + 2 * decode_tc_stages(d) * DT_BN) * (d + 8) * sizeof(__nv_bfloat16) + 2048;
+  const int by_smem = (int)((227 * 1024) / smem);
+  const int by_regs = d <= 64 ? 5 : 3;
+  return by_smem < by_regs ? (by_smem < 1 ? 1 : by_smem) : by_regs;
 }
 
 // 1 if this head size, page size and group size have an instantiation, else 0.

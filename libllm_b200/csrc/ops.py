@@ -369,6 +369,13 @@ def attention_decode_tc_supported(head_dim: int, page_size: int, group: int) -> 
     return bool(f(head_dim, page_size, group))
 
 
+def attention_decode_tc_ctas_per_sm(head_dim: int) -> int:
+    lib = build.load("attention_decode_tc")
+    f = lib.llm_attention_decode_tc_ctas_per_sm
+    f.argtypes, f.restype = [c_int], c_int
+    return int(f(head_dim))
+
+
 def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tensor, kcache: torch.Tensor,
                         vcache: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int,
                         n_kv: int, head_dim: int, page_size: int, chunk: int, n_splits: int, window: Optional[int],

@@ -84,12 +84,13 @@ def fused_decode_possible(ctx, cache, spec) -> bool:
                 and ops.attention_decode_tc_supported(spec.head_dim, cache.page_size, group))
 
 
-def fused_decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int) -> Tuple[int, int]:
-    """(chunk, n_splits) for the fused decode attention: about two and a half CTAs per SM (three fit),
-    each with at least a few pages so that its ring of tiles is worth filling; like ``decode_split``
-    it depends on the graph's bound on the length, not on the lengths themselves."""
+def fused_decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, head_dim: int = 64) -> Tuple[int, int]:
+    """(chunk, n_splits) for the fused decode attention: as many key splits as fill the GPU once
+    (all CTAs resident together: no second, partly filled wave), each of at least one page; like
+    ``decode_split`` it depends on the graph's bound on the length, not on the lengths themselves."""
     pairs = max(1, n_seqs * n_kv)
-    want = max(1, (5 * SM_COUNT // 2 + pairs - 1) // pairs)
+    slots = SM_COUNT * ops.attention_decode_tc_ctas_per_sm(head_dim)
+    want = max(1, slots // pairs)
     most = max(1, max_kv_len // page_size)
     n_splits = max(1, min(want, most))
     chunk = (max_kv_len + n_splits - 1) // n_splits
@@ -104,7 +105,8 @@ def fused_decode_attention(ctx, qkv: torch.Tensor, cache, spec, table: torch.Ten
     stacked product, [T, W] or [parts, T, W]."""
     if not fused_decode_possible(ctx, cache, spec) or qkv.dtype != torch.float32:
         return None
-    chunk, n_splits = fused_decode_split(ctx.n_seqs, spec.n_kv_heads, max(ctx.max_kv_len, 1), cache.page_size)
+    chunk, n_splits = fused_decode_split(ctx.n_seqs, spec.n_kv_heads, max(ctx.max_kv_len, 1), cache.page_size,
+                                         spec.head_dim)
     dev = qkv.device
     out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=torch.bfloat16, device=dev)
     ws_o = ws_ml = counters = None
