@@ -14,6 +14,7 @@
 // reads kv head h / (heads / kv_heads), scores are scaled by 1/sqrt(d), and one query sees
 // every cached key (src/flint/operators.cc:43-56, 115-124).
 #include "common.cuh"
+#include "attention_decode.h"
 #include <math.h>
 
 LLM_DEFINE_LAST_ERROR(llm_attention_decode_last_error)
@@ -302,4 +303,56 @@ LLM_EXPORT int llm_attention_decode(const void *q, long long q_stride, void *out
 #undef AD_CASES
 #undef AD_CASE
   LLM_FAIL("attention_decode: no kernel for head size %d, group %d", d, group);
+}
+
+
+// ---------------------------------------------------------------- the entry point that allocates nothing
+// Scratch of llm_attention_decode_static: the splits' unnormalised outputs, then their maxima and
+// sums.  It is part of the library's image on every GPU that loads it, until the process ends.
+static __device__ __align__(256) float g_decode_scratch[LLM_ATTENTION_DECODE_STATIC_FLOATS];
+
+// Device address of the scratch, looked up once per device.  In host code the array's name is
+// only a stand-in: the address a kernel may use comes from cudaGetSymbolAddress, asked with that
+// device current.
+static int static_scratch(float **out) {
+  constexpr int MAX_DEVICES = 64;
+  static float *ptrs[MAX_DEVICES] = {};
+  int dev = -1;
+  LLM_CHECK_CUDA(cudaGetDevice(&dev), "attention_decode_static: cudaGetDevice");
+  LLM_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "attention_decode_static: device %d is beyond the %d this entry point keeps track of", dev, MAX_DEVICES);
+  if (!ptrs[dev]) {
+    float *p = nullptr;
+    LLM_CHECK_CUDA(cudaGetSymbolAddress((void **)&p, g_decode_scratch), "attention_decode_static: cudaGetSymbolAddress");
+    LLM_REQUIRE(p != nullptr, "attention_decode_static: no device address for the scratch array");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return LLM_OK;
+}
+
+LLM_EXPORT long long llm_attention_decode_static_floats_needed(int n_seqs, int n_heads, int d, int n_splits) {
+  return n_splits <= 1 ? 0 : (long long)n_seqs * n_heads * n_splits * (d + 2);
+}
+
+LLM_EXPORT int llm_attention_decode_static(const void *q, long long q_stride, void *out, long long out_stride,
+                                           const void *kc, const void *vc, const int *tok_pos, const int *page_table,
+                                           int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
+                                           int chunk, int n_splits, int window, float scale, cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(n_seqs > 0 && n_heads > 0 && d > 0 && n_splits >= 1, "attention_decode_static: bad sizes");
+  const long long need = llm_attention_decode_static_floats_needed(n_seqs, n_heads, d, n_splits);
+  LLM_REQUIRE(need <= (long long)LLM_ATTENTION_DECODE_STATIC_FLOATS,
+              "attention_decode_static: %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of scratch, the built-in "
+              "array holds %lld; use fewer splits or sequences per call, or llm_attention_decode with scratch of your own",
+              n_seqs, n_heads, n_splits, d, need, (long long)LLM_ATTENTION_DECODE_STATIC_FLOATS);
+  float *ws_o = nullptr, *ws_ml = nullptr;
+  if (n_splits > 1) {
+    float *base = nullptr;
+    const int rc = static_scratch(&base);
+    if (rc != LLM_OK) return rc;
+    ws_o = base;
+    ws_ml = base + (size_t)n_seqs * n_heads * n_splits * d;
+  }
+  return llm_attention_decode(q, q_stride, out, out_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_heads, n_kv,
+                              d, page_size, chunk, n_splits, window, scale, ws_o, ws_ml, stream);
 }

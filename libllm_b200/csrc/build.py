@@ -37,7 +37,7 @@ FAMILIES: Dict[str, dict] = {
     "attention_generic": dict(sources=["attention_generic.cu"], headers=["common.cuh"]),
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
     "gemv": dict(sources=["gemv.cu"], headers=["common.cuh"]),
-    "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh"]),
+    "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh", "attention_decode.h"]),
     "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "gemm_tc": dict(sources=["gemm_tc.cu"], headers=["common.cuh"]),
     "attention_decode_tc": dict(sources=["attention_decode_tc.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
