@@ -156,8 +156,10 @@ def count_graph_launches(model, batch):
 
 
 def e2e_rate(model, batch, steps, warmup, vocab, seed=1):
-    """Decoded tokens a second through Model.generate: every step copies the step's token
-    ids and tables from pinned host memory to the device and reads the sampled ids back."""
+    """Decoded tokens a second through Model.generate, the call a user makes: token ids go in as
+    Python lists and come out as Python lists.  Every step copies its descriptor (positions, page
+    tables, token sources) from pinned host memory to the device and reads the sampled ids back;
+    the clock is the host's, stamped when a step's tokens have arrived."""
     import torch
     g = torch.Generator().manual_seed(seed)
     prompts = torch.randint(0, vocab, (batch, PROMPT), generator=g).tolist()
@@ -165,12 +167,10 @@ def e2e_rate(model, batch, steps, warmup, vocab, seed=1):
 
     def on_token(i, tok):
         if i == 0:
-            torch.cuda.synchronize()
             stamps.append(time.perf_counter())
 
-    from libllm_b200.engine import SamplingParams, generate
-    generate(model.engine, prompts, warmup + steps + 1, SamplingParams(0.0, 1, 1.0), seed=0, stop_tokens=[],
-             max_batch=batch, on_token=on_token)
+    model.generate(prompts, max_new_tokens=warmup + steps + 1, temperature=0.0, top_k=1, top_p=1.0, seed=0,
+                   stop_token_ids=[], max_batch=batch, on_token=on_token)
     # stamps[0] follows the prompt step; steps warmup+1 .. warmup+steps are timed
     t = stamps[warmup + steps] - stamps[warmup]
     graph = [v for k, v in model.engine._graphs.items() if k[0] == batch][-1]
@@ -202,12 +202,11 @@ def prefill_rate(model, vocab, flops_fn, peak_tflops, reps=3):
 
 
 def run_reference(args):
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
     print(json.dumps({"impl": "reference", "unavailable":
-                      "ling0322/libllm has no Python package to install offline (python/ holds a stale ctypes "
-                      "wrapper with no build; the C++ library needs a downloaded libunwind and a .llmpkg model "
-                      "exported from a checkpoint): nothing under baseline/_ref" if not os.path.isdir(ref_dir)
-                      else "baseline/_ref exists but holds no runnable benchmark of the reference"}))
+                      "ling0322/libllm's root is not pip-installable; its python/ folder installs only a ctypes "
+                      "wrapper (pylibllm) whose libllm.so is not built offline (CMake needs downloaded libunwind and "
+                      "FlashAttention sources) and whose symbols no longer exist in llm.h; models must be .llmpkg "
+                      "files exported from downloaded checkpoints"}))
     return 0
 
 

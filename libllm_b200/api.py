@@ -82,11 +82,12 @@ class Model:
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens=64, temperature: float = 1.0,
                  top_k: int = 50, top_p: float = 0.8, seed: int = 0,
-                 stop_token_ids: Optional[Iterable[int]] = None, max_batch: int = 64) -> List[List[int]]:
+                 stop_token_ids: Optional[Iterable[int]] = None, max_batch: int = 64,
+                 on_token=None) -> List[List[int]]:
         """Tokens generated for each prompt (lists of token ids in, lists out).
-        ``temperature=0`` is greedy."""
+        ``temperature=0`` is greedy; ``on_token(prompt index, token)`` is called as tokens arrive."""
         return _generate(self.engine, prompts, max_new_tokens, SamplingParams(temperature, top_k, top_p),
-                         seed, stop_token_ids, max_batch)
+                         seed, stop_token_ids, max_batch, on_token)
 
     def complete(self, prompt: Sequence[int], top_k: int = 50, top_p: float = 0.8,
                  temperature: float = 1.0, max_new_tokens: int = 1 << 30, seed: int = 0) -> Iterator[Chunk]:

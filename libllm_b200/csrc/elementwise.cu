@@ -13,11 +13,16 @@ LLM_DEFINE_LAST_ERROR(llm_elementwise_last_error)
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_kernel(const T *__restrict__ table, const int *__restrict__ tokens,
+                                 const int *__restrict__ fed_tokens, const int *__restrict__ fed_rows,
                                  float *__restrict__ out, int hidden, int vocab) {
   grid_dependents_launch();
   grid_dependency_wait();
   const int t = blockIdx.x;
+  // A token either comes with the step (tokens[t]) or is the one the previous step sampled for
+  // row fed_rows[t] of its batch, still on the device (fed_tokens): the host can then start this
+  // step before it has read that token back.
   int id = tokens[t];
+  if (fed_rows != nullptr && fed_rows[t] >= 0) id = fed_tokens[fed_rows[t]];
   // Token ids are checked on the host before they are uploaded; ids that the sampler
   // wrote on the device are below the vocabulary size by construction.  The clamp keeps
   // the read inside the table whatever happens.
@@ -27,15 +32,17 @@ __global__ void embedding_kernel(const T *__restrict__ table, const int *__restr
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
 }
 
-LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, float *out,
-                             int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, const int *fed_tokens,
+                             const int *fed_rows, float *out, int n_tokens, int hidden, int vocab,
+                             cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
+  LLM_REQUIRE((fed_tokens == nullptr) == (fed_rows == nullptr), "embedding: fed tokens come with their rows");
   int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == LLM_F32)
-    llm_launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, out, hidden, vocab);
+    llm_launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
   else if (dtype == LLM_BF16)
-    llm_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, out, hidden, vocab);
+    llm_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
   else
     LLM_FAIL("embedding: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("embedding");

@@ -69,16 +69,21 @@ def _call(family: str, name: str, argtypes, *args) -> None:
 
 
 # ------------------------------------------------------------------ elementwise
-def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = float(table[tokens[t], :]); out is the 32-bit residual stream."""
-    _on_gpu(table, tokens, out)
+def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor,
+              fed_tokens: Optional[torch.Tensor] = None, fed_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, :] = float(table[id_t, :]); out is the 32-bit residual stream.  id_t is tokens[t], or,
+    where fed_rows[t] >= 0, fed_tokens[fed_rows[t]]: a token the previous step left on the device."""
+    _on_gpu(table, tokens, out, fed_tokens, fed_rows)
     n = tokens.numel()
     assert tokens.dtype == torch.int32 and out.dtype == torch.float32
     assert table.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n, table.shape[1])
+    if fed_rows is not None:
+        assert fed_tokens is not None and fed_tokens.dtype == torch.int32 and fed_rows.dtype == torch.int32
+        assert fed_rows.numel() >= n
     _call("elementwise", "llm_embedding",
-          [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-          dtype_code(table.dtype), _ptr(table), _ptr(tokens), _ptr(out), n, table.shape[1], table.shape[0],
-          _stream())
+          [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+          dtype_code(table.dtype), _ptr(table), _ptr(tokens), _ptr(fed_tokens if fed_rows is not None else None),
+          _ptr(fed_rows), _ptr(out), n, table.shape[1], table.shape[0], _stream())
     return out
 
 

@@ -71,40 +71,50 @@ def generate(engine: Engine, prompts: Sequence[Sequence[int]], max_new_tokens,
     limits = [max_new_tokens] * n if isinstance(max_new_tokens, int) else list(max_new_tokens)
     if len(limits) != n:
         raise InvalidArgError("max_new_tokens: one number, or one per prompt")
-    stops = frozenset(engine.model.spec.stop_tokens if stop_tokens is None else stop_tokens)
+    stops_set = frozenset(engine.model.spec.stop_tokens if stop_tokens is None else stop_tokens)
     sampling.validate()
     out: List[List[int]] = [[] for _ in range(n)]
     capacity = engine.cache.n_pages * engine.page_size
     batches = plan_batches([len(p) for p in prompts], limits, capacity, max_batch, engine.page_size,
                            engine.max_seq_len)
-    host_tokens = None
     for batch in batches:
         live = [i for i in batch if limits[i] > 0]
         if not live:
             continue
         slots = {i: engine.open_sequence() for i in live}
         try:
-            feed = {i: list(prompts[i]) for i in live}
+            # The step that is running on the device: (request ids in row order, pending tokens).
+            # While the host waits for its tokens, the next step is already queued behind it with
+            # every sequence that can still go on; it takes its tokens from the device.  A
+            # sequence that turns out to have ended (a stop token) has then run one step too
+            # many: its result is dropped and its slot is given back, nothing else sees it.
             produced = {i: 0 for i in live}
-            while live:
-                items = [StepItem(slots[i], feed[i], [len(feed[i]) - 1]) for i in live]
-                uni = [uniform(seed, i, produced[i]) for i in live]
-                _, tokens = engine.step(items, sampling, uni, return_logits=False)
-                host = tokens.cpu().tolist()           # the one device-to-host read of the step
-                nxt = []
-                for i, tok in zip(live, host):
-                    ends, emit = should_stop(tok, produced[i], limits[i], stops)
+            items = [StepItem(slots[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in live]
+            running = (live, engine.step_tokens(items, sampling, [uniform(seed, i, 0) for i in live]))
+            ended = set()
+            while running is not None:
+                ids, pending = running
+                # queue the next step: the sequences of this one that have not reached their count
+                ahead = [(row, i) for row, i in enumerate(ids) if i not in ended and produced[i] + 1 < limits[i]]
+                nxt = None
+                if ahead:
+                    items = [StepItem(slots[i], [0], [0], fed_row=row) for row, i in ahead]
+                    uni = [uniform(seed, i, produced[i] + 1) for _, i in ahead]
+                    nxt = ([i for _, i in ahead], engine.step_tokens(items, sampling, uni))
+                # now this step's tokens (the one device-to-host read of the step)
+                for i, tok in zip(ids, pending.result()):
+                    if i in ended:
+                        continue                    # it ran one step beyond its end
+                    stops, emit = should_stop(tok, produced[i], limits[i], stops_set)
                     if emit:
                         out[i].append(tok)
                         produced[i] += 1
                         if on_token is not None:
                             on_token(i, tok)
-                    if ends:
+                    if stops:
+                        ended.add(i)
                         engine.close_sequence(slots.pop(i))
-                    else:
-                        feed[i] = [tok]
-                        nxt.append(i)
-                live = nxt
+                running = nxt
         finally:
             for s in slots.values():
                 engine.close_sequence(s)

@@ -131,7 +131,8 @@ class Model:
     # ---------------------------------------------------------------- one step
     def forward(self, ctx: StepContext, cache, page_tables: List[torch.Tensor]) -> torch.Tensor:
         resid = torch.empty((ctx.n_tokens, self.spec.hidden), dtype=torch.float32, device=self.device)
-        ops.embedding(self.embedding, ctx.tokens, resid)
+        fed = ctx.extras.get("fed")          # (tokens of the previous step on the device, row per token)
+        ops.embedding(self.embedding, ctx.tokens, resid, *(fed or ()))
         stream = ResidualStream(resid)
         for i, e in enumerate(self.spec.schedule):
             view = cache.layer_cache(i, e.cache_from, page_tables)

@@ -33,6 +33,7 @@ class StepItem:
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    fed_row: Optional[int] = None      # its one token is the one the previous step sampled for this row
 
 
 @dataclass(frozen=True)
@@ -73,7 +74,7 @@ class _Descriptor:
     def __init__(self, device, n_tokens: int, n_seqs: int, n_want: int, widths: List[int]):
         self.n_tokens, self.n_seqs, self.n_want, self.widths = n_tokens, n_seqs, n_want, widths
         T, B, W = n_tokens, n_seqs, n_want
-        sizes = [T, T, T, B + 1, B, B, W, B] + [B * w for w in widths]
+        sizes = [T, T, T, B + 1, B, B, W, B, T] + [B * w for w in widths]
         self.offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(int)
         total = int(self.offsets[-1])
         self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
@@ -116,6 +117,12 @@ class Engine:
         self.cache = KVCache(model.run_cache_needs(), model.run_state_needs(), max_tokens, self.dtype,
                              self.device, page_size, max_slots)
         self.vocab = model.spec.vocab_size
+        # The tokens the last sampling step drew, kept on the device: the next step can take them
+        # from here (StepItem.fed_row) while the host is still reading them back.
+        self.last_tokens = torch.zeros(max(self.max_step_tokens, 1024), dtype=torch.int32, device=self.device)
+        self._token_buffers = [torch.empty(self.last_tokens.numel(), dtype=torch.int32, pin_memory=True)
+                               for _ in range(4)]
+        self._token_turn = 0
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
         self._eager_desc: Dict[tuple, _Descriptor] = {}
         self.launch_log: Optional[List[str]] = None
@@ -161,6 +168,28 @@ class Engine:
         self.steps_run += 1
         return out
 
+    def step_tokens(self, items: Sequence[StepItem], sampling: SamplingParams,
+                    uniforms: Optional[Sequence[float]] = None) -> "PendingTokens":
+        """Runs a step that samples one token per item (each wants exactly one place) and returns
+        at once: the tokens stay on the device in ``last_tokens`` (row i = item i), where the next
+        step's items may take them from (``StepItem.fed_row``), and are on their way to pinned
+        host memory; ``PendingTokens.result()`` waits for that copy."""
+        items = list(items)
+        if any(len(it.want) != 1 for it in items):
+            raise InvalidArgError("step_tokens: every item wants exactly one place")
+        n = len(items)
+        if n > self.last_tokens.numel():
+            raise InvalidArgError(f"step_tokens: {n} sequences, at most {self.last_tokens.numel()} are taken")
+        _, tokens = self.step(items, sampling, uniforms, return_logits=False)
+        if tokens.data_ptr() != self.last_tokens.data_ptr():
+            self.last_tokens[:n].copy_(tokens)
+        host = self._token_buffers[self._token_turn]
+        self._token_turn = (self._token_turn + 1) % len(self._token_buffers)
+        host[:n].copy_(self.last_tokens[:n], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return PendingTokens(n, host, done)
+
     def _validate(self, items: Sequence[StepItem]) -> None:
         seen = set()
         for it in items:
@@ -174,9 +203,13 @@ class Engine:
             if past + n > self.max_seq_len:
                 raise InvalidArgError(f"slot {it.slot}: {past} + {n} tokens exceed the longest sequence "
                                       f"this engine holds ({self.max_seq_len})")
-            for t in it.tokens:
-                if not 0 <= int(t) < self.vocab:
-                    raise InvalidArgError(f"slot {it.slot}: token id {t} outside the vocabulary ({self.vocab})")
+            if it.fed_row is not None:
+                if n != 1 or not 0 <= it.fed_row < self.last_tokens.numel():
+                    raise InvalidArgError(f"slot {it.slot}: a fed token is one token from a row of the last step")
+            else:
+                for t in it.tokens:
+                    if not 0 <= int(t) < self.vocab:
+                        raise InvalidArgError(f"slot {it.slot}: token id {t} outside the vocabulary ({self.vocab})")
             for w in it.want:
                 if not 0 <= int(w) < n:
                     raise InvalidArgError(f"slot {it.slot}: wanted place {w} outside the {n} tokens given")
@@ -187,11 +220,16 @@ class Engine:
         desc.wait_host_free()
         tokens, tok_seq, tok_pos = desc.field(0), desc.field(1), desc.field(2)
         seq_start, seq_past, seq_slot = desc.field(3), desc.field(4), desc.field(5)
-        want, uni = desc.field(6), desc.field(7)
+        want, uni, fed = desc.field(6), desc.field(7), desc.field(8)
         o = 0
         for b, p in enumerate(pieces):
-            toks = items[p.index].tokens[p.start:p.start + p.count]
-            tokens[o:o + p.count] = toks
+            it = items[p.index]
+            if it.fed_row is not None:
+                tokens[o] = 0
+                fed[o] = it.fed_row
+            else:
+                tokens[o:o + p.count] = it.tokens[p.start:p.start + p.count]
+                fed[o:o + p.count] = -1
             tok_seq[o:o + p.count] = b
             tok_pos[o:o + p.count] = np.arange(p.past + p.start, p.past + p.start + p.count)
             seq_start[b] = o
@@ -204,7 +242,7 @@ class Engine:
             uni.view(np.float32)[:len(uniforms)] = np.asarray(uniforms, dtype=np.float32)
         slots = [p.slot for p in pieces]
         for g, w in enumerate(desc.widths):
-            desc.field(8 + g).reshape(len(pieces), w)[:] = self.cache.page_table(g, slots, w)
+            desc.field(9 + g).reshape(len(pieces), w)[:] = self.cache.page_table(g, slots, w)
         desc.upload()
 
     def _context(self, desc: _Descriptor, pieces: List[_Piece], n_want: int, decode_only: bool,
@@ -218,11 +256,16 @@ class Engine:
             past_lens=[p.past + p.start for p in pieces], slots=[p.slot for p in pieces],
             max_q_len=max(p.count for p in pieces), max_kv_len=max_kv_len, decode_only=decode_only)
         ctx.extras["uniforms"] = desc.field(7, True).view(torch.float32)
-        tables = [desc.field(8 + g, True).view(B, w) for g, w in enumerate(desc.widths)]
+        ctx.extras["fed"] = (self.last_tokens, desc.field(8, True))
+        tables = [desc.field(9 + g, True).view(B, w) for g, w in enumerate(desc.widths)]
         return ctx, tables
 
-    def _sample(self, logits: torch.Tensor, sampling: SamplingParams, uniforms: torch.Tensor) -> torch.Tensor:
-        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+    def _sample(self, logits: torch.Tensor, sampling: SamplingParams, uniforms: torch.Tensor,
+                into_last: bool = False) -> torch.Tensor:
+        if into_last and logits.shape[0] <= self.last_tokens.numel():
+            out = self.last_tokens[:logits.shape[0]]
+        else:
+            out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
         if sampling.temperature == 0:
             return ops.argmax(logits, out)
         return ops.sample(logits, sampling.temperature, sampling.top_k, sampling.top_p, uniforms, out)
@@ -334,6 +377,17 @@ class Engine:
         return (logits if return_logits else None), tokens
 
 
+class PendingTokens:
+    """Tokens of a step on their way from the device to the host."""
+
+    def __init__(self, n: int, host: torch.Tensor, done: "torch.cuda.Event"):
+        self.n, self._host, self._done = n, host, done
+
+    def result(self) -> List[int]:
+        self._done.synchronize()
+        return self._host[:self.n].tolist()
+
+
 class _DecodeGraph:
     """A captured step of B sequences bringing one token each, page tables ``width`` wide."""
 
@@ -351,7 +405,7 @@ class _DecodeGraph:
         logits = eng.model.forward(ctx, eng.cache, tables)
         tokens = None
         if self.sampling is not None:
-            tokens = eng._sample(logits, self.sampling, ctx.extras["uniforms"])
+            tokens = eng._sample(logits, self.sampling, ctx.extras["uniforms"], into_last=True)
         return logits, tokens
 
     def run(self) -> None:

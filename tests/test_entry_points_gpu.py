@@ -215,3 +215,28 @@ def test_trace_run_whole_last_32_and_unequal_batches(name, dtype, tmp_path):
         for j, n in enumerate(lens):
             toks = tokens_for(name, n + n_dec - j, 910 + 10 * b + j)
             check_logits(got[f"b{b}r{j}"], P.forward_logits(c, w, toks), dtype, f"trace b{b}r{j}")
+
+
+def test_tokens_fed_on_the_device_give_the_same_steps_as_tokens_from_the_host():
+    """A step whose tokens are the ones the previous step left on the device (fed rows, in another
+    order and for a subset) computes what the same step computes from token ids the host sends."""
+    from libllm_b200.engine import GREEDY, StepItem
+    model, c, w = entry_model("B", "float32")
+    eng = model.engine
+    prompts = [tokens_for("B", n, 950 + n) for n in (9, 30, 4)]
+    runs = []
+    for fed in (False, True):
+        slots = [eng.open_sequence() for _ in prompts]
+        first = eng.step_tokens([StepItem(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)], GREEDY)
+        if fed:         # rows 2 and 0 go on, taken from the device before the host has looked at them
+            nxt = eng.step_tokens([StepItem(slots[2], [0], [0], fed_row=2), StepItem(slots[0], [0], [0], fed_row=0)], GREEDY)
+            toks = first.result()
+        else:
+            toks = first.result()
+            nxt = eng.step_tokens([StepItem(slots[2], [toks[2]], [0]), StepItem(slots[0], [toks[0]], [0])], GREEDY)
+        runs.append((toks, nxt.result()))
+        for s in slots:
+            eng.close_sequence(s)
+    assert runs[0] == runs[1]
+    want = [P.greedy_continuation(c, w, p, 2) for p in prompts]
+    assert runs[0][0] == [x[0] for x in want] and runs[0][1] == [want[2][1], want[0][1]]
