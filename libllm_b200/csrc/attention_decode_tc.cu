@@ -27,7 +27,6 @@
 
 LLM_DEFINE_LAST_ERROR(llm_attention_decode_tc_last_error)
 
-constexpr int DT_WARPS = 4;
 constexpr int DT_BN = 64;      // keys per tile = tokens per page
 constexpr int DT_ROWS = 16;    // rows of the MMA tile: query heads of one group
 
@@ -36,7 +35,11 @@ constexpr int DT_ROWS = 16;    // rows of the MMA tile: query heads of one group
 // step's CTAs all fit on the GPU at once instead of running in one and a bit waves.
 __host__ __device__ constexpr int decode_tc_stages(int d) { return 2; }
 
-template <int D>
+// DT_WARPS warps share a tile's 64 keys (64 / DT_WARPS each, a running maximum and sum per warp,
+// joined at the end).  Four warps run: with one warp per CTA (no waiting for other warps at a
+// tile) 64 sequences take as long, and 1 or 8 take up to twice as long (measured), because the
+// rotation, the copies' issue and the joining are then one warp's work.
+template <int D, int DT_WARPS>
 __global__ void __launch_bounds__(DT_WARPS * 32, D <= 64 ? 5 : 3)
 attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, int qkv_parts,
                            long long qkv_part_stride, const float *__restrict__ table,
@@ -51,6 +54,8 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   constexpr int KS = D / 16;
   constexpr int DT = D / 8;
   constexpr int NS = decode_tc_stages(D);                    // key tiles in flight
+  constexpr int KW = DT_BN / DT_WARPS;                       // keys of a tile per warp
+  constexpr int NTW = KW / 8;                                // its score tiles of 8 keys
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16 *sQ = reinterpret_cast<__nv_bfloat16 *>(smem_raw);           // [16][LD]
   __nv_bfloat16 *sNew = sQ + DT_ROWS * LD;                                    // [2][LD]: new k, new v
@@ -222,33 +227,39 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], sQ + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8);
     }
-    // this warp's 16 keys of the tile
-    const int k0 = kt * DT_BN + warp * 16;
-    if (k0 < c1 && k0 + 16 > kstart) {
-      float s[2][4];
+    // this warp's keys of the tile
+    const int k0 = kt * DT_BN + warp * KW;
+    if (k0 < c1 && k0 + KW > kstart) {
+      float s[NTW][4];
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
+      for (int n = 0; n < NTW; ++n)
 #pragma unroll
         for (int j = 0; j < 4; ++j) s[n][j] = 0.f;
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-        unsigned kb[4];
-        ldmatrix_x4(kb, tk + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
-        mma16816(s[0], qf[ks], kb[0], kb[1]);
-        mma16816(s[1], qf[ks], kb[2], kb[3]);
-      }
-      if (k0 + 16 > c1 || k0 < kstart) {
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+        for (int n2 = 0; n2 < NTW / 2; ++n2) {
+          unsigned kb[4];
+          ldmatrix_x4(kb, tk + (warp * KW + n2 * 16 + (lane & 7) + (lane >> 4) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+          mma16816(s[2 * n2], qf[ks], kb[0], kb[1]);
+          mma16816(s[2 * n2 + 1], qf[ks], kb[2], kb[3]);
+        }
+      }
+      if (k0 + KW > c1 || k0 < kstart) {
+#pragma unroll
+        for (int n = 0; n < NTW; ++n)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int key = k0 + n * 8 + 2 * t + (j & 1);
             if (key >= c1 || key < kstart) s[n][j] = -INFINITY;
           }
       }
-      float mx[2];
-      mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-      mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < NTW; ++n) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+      }
       float alpha[2], moff[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
@@ -261,7 +272,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
       }
       float sum[2] = {0.f, 0.f};
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < NTW; ++n) {
         s[n][0] = exp2f(fmaf(s[n][0], scale_log2, -moff[0]));
         s[n][1] = exp2f(fmaf(s[n][1], scale_log2, -moff[0]));
         s[n][2] = exp2f(fmaf(s[n][2], scale_log2, -moff[1]));
@@ -278,17 +289,20 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
         o[i][2] *= alpha[1];
         o[i][3] *= alpha[1];
       }
-      unsigned pa[4];
-      pa[0] = pack_bf16(s[0][0], s[0][1]);
-      pa[1] = pack_bf16(s[0][2], s[0][3]);
-      pa[2] = pack_bf16(s[1][0], s[1][1]);
-      pa[3] = pack_bf16(s[1][2], s[1][3]);
 #pragma unroll
-      for (int d2 = 0; d2 < DT / 2; ++d2) {
-        unsigned vb[4];
-        ldmatrix_x4_trans(vb, tv + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + d2 * 16 + (lane >> 4) * 8);
-        mma16816(o[2 * d2], pa, vb[0], vb[1]);
-        mma16816(o[2 * d2 + 1], pa, vb[2], vb[3]);
+      for (int kk = 0; kk < KW / 16; ++kk) {
+        unsigned pa[4];
+        pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < DT / 2; ++d2) {
+          unsigned vb[4];
+          ldmatrix_x4_trans(vb, tv + (warp * KW + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + d2 * 16 + (lane >> 4) * 8);
+          mma16816(o[2 * d2], pa, vb[0], vb[1]);
+          mma16816(o[2 * d2 + 1], pa, vb[2], vb[3]);
+        }
       }
     }
     __syncthreads();                     // every warp is done with the stage
@@ -298,7 +312,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   cp_async_wait<0>();
   __syncthreads();
 
-  // Join the four warps (each saw other keys): through shared memory, in warp order.
+  // Join the warps (each saw other keys): through shared memory, in warp order.
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
@@ -390,7 +404,8 @@ static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_part
   const size_t tiles = (size_t)(DT_ROWS + 2 + 2 * decode_tc_stages(D) * DT_BN) * LD * sizeof(__nv_bfloat16);
   const size_t smem = tiles + (size_t)(chunk / DT_BN + 2) * sizeof(int);
   LLM_REQUIRE(smem <= 200 * 1024, "attention_decode_tc: a chunk of %d keys spans too many pages", chunk);
-  auto kern = attention_decode_tc_kernel<D>;
+  constexpr int DT_WARPS = 4;
+  auto kern = attention_decode_tc_kernel<D, DT_WARPS>;
   if (smem > 48 * 1024)
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    "attention_decode_tc attribute");

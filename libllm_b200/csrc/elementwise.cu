@@ -155,12 +155,19 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
                               const float *weight, float eps, void *out, const int *rows, int n_rows,
                               int hidden, cudaStream_t stream) {
   constexpr int THREADS = 256;
-  constexpr int VPT = 4, MAXP = 8;
+  constexpr int VPT = 4;
   const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
                        (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
-  if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= MAXP) {
-    llm_launch(add_rmsnorm_vec_kernel<TD, TO, THREADS, VPT, MAXP>, n_rows, THREADS, 0, stream, resid,
-               (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden);
+  if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= 8) {
+    // one instantiation per bound on the parts: registers for eight parts cost a prompt step
+    // (one part, thousands of rows) a third of its speed
+#define ADDNORM_GO(MAXP)                                                                                 \
+  llm_launch(add_rmsnorm_vec_kernel<TD, TO, THREADS, VPT, MAXP>, n_rows, THREADS, 0, stream, resid,      \
+             (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden)
+    if (n_parts <= 1) ADDNORM_GO(1);
+    else if (n_parts <= 4) ADDNORM_GO(4);
+    else ADDNORM_GO(8);
+#undef ADDNORM_GO
     LLM_CHECK_LAUNCH("add_rmsnorm");
     return LLM_OK;
   }
@@ -215,22 +222,43 @@ __global__ void swiglu_kernel(const TI *__restrict__ gu, T *__restrict__ out, in
   }
 }
 
+// Four values per thread (widths that are a multiple of 4, 16-byte aligned rows).
+template <typename TI, typename T>
+__global__ void swiglu_vec_kernel(const TI *__restrict__ gu, T *__restrict__ out, int inter4, size_t total4) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter4;
+    const int i = (int)(idx - t * inter4) * 4;
+    const TI *row = gu + t * 8 * (size_t)inter4;
+    const float4 g = ld4(row + i), u = ld4(row + 4 * (size_t)inter4 + i);
+    st4(out + idx * 4, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
+                                   g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+  }
+}
+
 LLM_EXPORT int llm_swiglu(int in_dtype, int dtype, const void *gu, void *out, int n_tokens, int inter,
                           cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
-  const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
+  const bool vec = inter % 4 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0;
+  const size_t total = vec ? (size_t)n_tokens * (inter / 4) : (size_t)n_tokens * inter;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  if (in_dtype == LLM_F32 && dtype == LLM_F32)
-    llm_launch(swiglu_kernel<float, float>, (unsigned)blocks, threads, 0, stream, (const float *)gu, (float *)out, inter, total);
-  else if (in_dtype == LLM_F32 && dtype == LLM_BF16)
-    llm_launch(swiglu_kernel<float, __nv_bfloat16>, (unsigned)blocks, threads, 0, stream, (const float *)gu, (__nv_bfloat16 *)out, inter, total);
-  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16)
-    llm_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, (unsigned)blocks, threads, 0, stream, (const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, inter, total);
-  else
-    LLM_FAIL("swiglu: unsupported dtypes in %d out %d", in_dtype, dtype);
+#define SWIGLU_GO(TI, T)                                                                                     \
+  do {                                                                                                       \
+    if (vec)                                                                                                 \
+      llm_launch(swiglu_vec_kernel<TI, T>, (unsigned)blocks, threads, 0, stream, (const TI *)gu, (T *)out, inter / 4, total); \
+    else                                                                                                     \
+      llm_launch(swiglu_kernel<TI, T>, (unsigned)blocks, threads, 0, stream, (const TI *)gu, (T *)out, inter, total); \
+  } while (0)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) SWIGLU_GO(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) SWIGLU_GO(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) SWIGLU_GO(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("swiglu: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef SWIGLU_GO
   LLM_CHECK_LAUNCH("swiglu");
   return LLM_OK;
 }

@@ -62,14 +62,15 @@ def test_add_rmsnorm(dtype, hidden, parts):
 
 
 @pytest.mark.parametrize("dtype,in_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
-def test_swiglu(dtype, in_dtype):
+@pytest.mark.parametrize("inter", [173, 176])        # the general kernel, and four values per thread
+def test_swiglu(dtype, in_dtype, inter):
     from libllm_b200.csrc import ops
-    gu = rnd((9, 2 * 173), in_dtype, 5, 2.0)
+    gu = rnd((9, 2 * inter), in_dtype, 5, 2.0)
     gu[0, 0] = -30.0
     gu[0, 1] = 30.0
-    out = torch.empty((9, 173), dtype=DT[dtype], device=DEV)
+    out = torch.empty((9, inter), dtype=DT[dtype], device=DEV)
     ops.swiglu(gu, out)
-    close(out, P.swiglu(gu[:, :173].cpu(), gu[:, 173:].cpu()), dtype)
+    close(out, P.swiglu(gu[:, :inter].cpu(), gu[:, inter:].cpu()), dtype)
 
 
 @pytest.mark.parametrize("dtype,out_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
