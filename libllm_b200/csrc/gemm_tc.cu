@@ -130,26 +130,35 @@ __host__ __device__ constexpr unsigned instr_desc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
-template <int TN>
+// SW: 0 plain product; 1 SwiGLU with gate and up rows interleaved in one 128-row tile (64 + 64,
+// handed over between epilogue warps: steps of few tokens, where a tile per SM matters); 2 SwiGLU with
+// a tile of 128 gate rows and one of 128 up rows per stage and an accumulator for each, so that a
+// lane holds both values of a feature (prompt steps).
+template <int TN, int SW>
 struct TcShape {
+  static constexpr int A_TILES = SW == 2 ? 2 : 1;
+  static constexpr int A_BYTES = A_TILES * TC_A_BYTES;
   static constexpr int B_BYTES = TN * TC_BK * 2;
-  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // Steps of few tokens (TN <= 64) take half of an SM's shared memory, so that the CTA of the next
   // product in the stream can move in beside this one and fill its ring with weights while this
   // one finishes; prompt steps take a ring as deep as fits.
   static constexpr int BUDGET = TN <= 64 ? 100 * 1024 : 200 * 1024;
   static constexpr int STAGES = BUDGET / STAGE_BYTES;
-  static constexpr int TMEM_COLS = 2 * TN < 32 ? 32 : 2 * TN;          // two accumulators; a power of two
+  static constexpr int ACC_COLS = A_TILES * TN;                          // columns of one accumulator buffer
+  static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // two buffers; a power of two
   static constexpr int XCH_BYTES = 64 * 17 * 4;                        // SwiGLU hand-over: 64 rows x 16 tokens (+1 pad)
   static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + XCH_BYTES + 256;
+  static_assert(TMEM_COLS <= 512, "the accumulators do not fit tensor memory");
 };
 
-template <int TN, bool SWIGLU, typename TO>
+template <int TN, int SW, typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO *__restrict__ out, long long ldo, int M, int n_out, int K, int row_tiles, int tok_tiles,
                int k_parts, int kb_per_part, long long part_stride, int *status) {
-  using S = TcShape<TN>;
+  using S = TcShape<TN, SW>;
+  constexpr bool SWIGLU = SW == 1;                      // the interleaved tile with the hand-over
   constexpr int STAGES = S::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -193,7 +202,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int n_tiles = row_tiles * tok_tiles * k_parts;
   const int n_kblocks_total = (K + TC_BK - 1) / TC_BK;
-  constexpr int ROWS_OUT = SWIGLU ? 64 : 128;              // output features per tile
+  constexpr int ROWS_OUT = SW == 1 ? 64 : 128;             // output features per tile
 
   if (warp == 0) {
     // ------------------------------------------------------------ loader
@@ -212,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         w.kb = part * kb_per_part;
         w.kb1 = min(n_kblocks_total, w.kb + kb_per_part);
         w.row_a = row_tile * ROWS_OUT;
-        w.row_b = SWIGLU ? n_out + w.row_a : w.row_a + 64;
+        w.row_b = SW != 0 ? n_out + w.row_a : w.row_a + 64;
       };
       auto next = [&](Walk &w) {
         if (++w.kb >= w.kb1) start(w, w.tile + gridDim.x);
@@ -220,11 +229,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       auto load_w = [&](const Walk &w, int stage) {
         const unsigned dst = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
         mbar_expect_tx(bar_full + 8 * stage, S::STAGE_BYTES);
-        tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
-        tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
+        if (SW == 2) {                    // 128 gate rows, then 128 up rows
+          tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
+          tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_a + 64, bar_full + 8 * stage);
+          tma_load_2d(dst + TC_A_BYTES, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
+          tma_load_2d(dst + TC_A_BYTES + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b + 64, bar_full + 8 * stage);
+        } else {
+          tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
+          tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
+        }
       };
       auto load_x = [&](const Walk &w, int stage) {
-        tma_load_2d(smem_u32(smem + (size_t)stage * S::STAGE_BYTES) + TC_A_BYTES, &map_x, w.kb * TC_BK,
+        tma_load_2d(smem_u32(smem + (size_t)stage * S::STAGE_BYTES) + S::A_BYTES, &map_x, w.kb * TC_BK,
                     w.tok_tile * TN, bar_full + 8 * stage);
       };
       // Weights first: they do not depend on the kernel before this one, so the whole ring
@@ -276,17 +292,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2);
         if (!ok) break;
         tc_fence_after();
-        const unsigned d_tmem = tmem_base + acc * TN;
+        const unsigned d_tmem = tmem_base + acc * S::ACC_COLS;
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3);
           if (!ok) break;
           tc_fence_after();
           const unsigned a_addr = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
-          const unsigned long long a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + TC_A_BYTES);
+          const unsigned long long a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + S::A_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < TC_BK / 16; ++kk)    // 16 k = 32 bytes further along the swizzled row
+          for (int kk = 0; kk < TC_BK / 16; ++kk) {  // 16 k = 32 bytes further along the swizzled row
             tc_mma(d_tmem, a_desc + (unsigned long long)(kk * 2), b_desc + (unsigned long long)(kk * 2), IDESC,
                    (kb > kb0 || kk > 0) ? 1u : 0u);
+            if (SW == 2)                             // the up rows into the accumulator beside
+              tc_mma(d_tmem + TN, smem_desc(a_addr + TC_A_BYTES) + (unsigned long long)(kk * 2),
+                     b_desc + (unsigned long long)(kk * 2), IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
           tc_commit(bar_empty + 8 * stage);          // the stage is free when these products have read it
           if (++stage == STAGES) {
             stage = 0;
@@ -318,8 +338,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll 1
       for (int c0 = 0; c0 < TN && ok; c0 += 16, ++n_chunk) {
         float v[16];
-        tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * TN + c0), v);
-        if (SWIGLU) {
+        tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * S::ACC_COLS + c0), v);
+        if (SW == 2) {
+          float u[16];
+          tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * S::ACC_COLS + TN + c0), u);
+          const int f = row_tile * 128 + row_in_tile;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int tok = tok0 + c0 + i;
+            const float g = v[i];
+            if (f < n_out && tok < M) o[(size_t)tok * ldo + f] = from_float<TO>(g / (1.f + expf(-g)) * u[i]);
+          }
+        } else if (SWIGLU) {
           // The upper two warps (up rows) hand their values to the lower two (gate rows of the
           // same features) through shared memory; both directions are barriers with a time limit.
           if (quarter >= 2) {
@@ -447,12 +477,12 @@ int sm_count() {
   return n;
 }
 
-template <int TN, bool SWIGLU, typename TO>
+template <int TN, int SW, typename TO>
 int launch_tc(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N, int K, int k_parts,
               long long part_stride, int *status, cudaStream_t stream) {
-  using S = TcShape<TN>;
-  const int n_out = SWIGLU ? N / 2 : N;
-  const int rows_out = SWIGLU ? 64 : 128;
+  using S = TcShape<TN, SW>;
+  const int n_out = SW != 0 ? N / 2 : N;
+  const int rows_out = SW == 1 ? 64 : 128;
   const int row_tiles = (n_out + rows_out - 1) / rows_out;
   const int tok_tiles = (M + TN - 1) / TN;
   const int n_kblocks = (K + TC_BK - 1) / TC_BK;
@@ -463,7 +493,7 @@ int launch_tc(const void *x, long long ldx, const void *W, void *out, long long 
   if (rc != LLM_OK) return rc;
   rc = get_map(x, M, K, ldx, TN, &map_x);
   if (rc != LLM_OK) return rc;
-  auto kern = gemm_tc_kernel<TN, SWIGLU, TO>;
+  auto kern = gemm_tc_kernel<TN, SW, TO>;
   static bool attr_set = false;
   if (!attr_set) {
     LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM), "gemm_tc attribute");
@@ -481,12 +511,18 @@ int launch_tc(const void *x, long long ldx, const void *W, void *out, long long 
 template <bool SWIGLU, typename TO>
 int dispatch_tc(const void *x, long long ldx, const void *W, void *out, long long ldo, int M, int N, int K, int k_parts,
                 long long part_stride, int *status, cudaStream_t stream) {
-#define TC_GO(TN) return launch_tc<TN, SWIGLU, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream)
-  if (M <= 16) TC_GO(16);
-  if (M <= 32) TC_GO(32);
-  if (M <= 64) TC_GO(64);
-  if (M <= 128) TC_GO(128);
-  TC_GO(256);
+#define TC_GO(TN, SW) return launch_tc<TN, SW, TO>(x, ldx, W, out, ldo, M, N, K, k_parts, part_stride, status, stream)
+  if (SWIGLU) {
+    if (M <= 16) TC_GO(16, 1);
+    if (M <= 32) TC_GO(32, 1);
+    if (M <= 64) TC_GO(64, 1);
+    TC_GO(128, 2);
+  }
+  if (M <= 16) TC_GO(16, 0);
+  if (M <= 32) TC_GO(32, 0);
+  if (M <= 64) TC_GO(64, 0);
+  if (M <= 128) TC_GO(128, 0);
+  TC_GO(256, 0);
 #undef TC_GO
 }
 

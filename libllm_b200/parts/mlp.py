@@ -33,7 +33,11 @@ class SwiGLU(FeedForward):
         return ["elementwise", "gemm_plain", "gemv", "gemm_tc"]
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
-        m = fast.small_batch_linear(x, self.w_gate_up, ctx.dtype, swiglu=True) if x.dtype == torch.bfloat16 else None
+        m = None
+        if x.dtype == torch.bfloat16:
+            m = fast.small_batch_linear(x, self.w_gate_up, ctx.dtype, swiglu=True)
+            if m is None:
+                m = fast.fused_gate_up(x, self.w_gate_up, ctx.dtype)
         if m is not None:
             return linear(m, self.w_down, out_dtype=torch.float32, parts_ok=True)
         gu = linear(x, self.w_gate_up, out_dtype=torch.float32)

@@ -437,7 +437,8 @@ def test_tensor_core_product_in_parts_of_k(M, N, K, parts):
     assert 1 <= ops.gemm_tc_suggest_parts(M, N, K) <= 8
 
 
-@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (5, 173, 80), (8, 8192, 2048), (40, 300, 256), (200, 128, 136)])
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (5, 173, 80), (8, 8192, 2048), (40, 300, 256), (200, 128, 136), (257, 391, 200),
+                                   (1000, 1024, 512)])
 def test_tensor_core_product_with_swiglu(M, I, K):
     from libllm_b200.csrc import ops
     x = rnd((M, K), "bfloat16", 54)
