@@ -162,14 +162,14 @@ def bench_attention_decode(args, timer):
         ang = torch.arange(ctx + 1, device="cuda", dtype=torch.float64)[:, None] * \
             (10000.0 ** (-torch.arange(0, d, 2, device="cuda", dtype=torch.float64) / d))[None]
         rope = torch.cat([ang.cos(), ang.sin()], 1).float().contiguous()
-        chunk, n_splits = fast.fused_decode_split(B, nKV, table.shape[1] * 64, 64, d)
+        chunk, n_splits = 0, fast.fused_decode_splits(B, nKV, table.shape[1] * 64, 64, d)
         ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
         ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
         counters = torch.zeros(B * nKV, dtype=torch.int32, device="cuda")
 
         def fn():
             ops.attention_decode_tc(qkv, out, rope, k, v, pos, table, nH, nKV, d, 64, chunk, n_splits, None, scale,
-                                    True, ws_o, ws_ml, counters)
+                                    True, ws_o, ws_ml, counters, max_len=table.shape[1] * 64)
         name = "attention_decode_tc (rotation, append, attention, join)"
     us = timer.run(fn)
     report(name, us, bytes_moved=nbytes, flops=4 * B * nH * ctx * d, batch=B, context=ctx, heads=nH, kv_heads=nKV,

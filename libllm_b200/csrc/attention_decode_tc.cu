@@ -70,6 +70,9 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   const int pos = tok_pos[b];
   const int len = pos + 1;
   const int kstart = window > 0 ? max(0, len - window) : 0;
+  // chunk 0: the sequence's own length cut into n_splits runs of whole pages, so that every split
+  // has work whatever bound on the length the launch was shaped for
+  if (chunk <= 0) chunk = max(DT_BN, ((len + n_splits - 1) / n_splits + DT_BN - 1) / DT_BN * DT_BN);
   const int c0 = split * chunk;
   const int c1 = min(c0 + chunk, len);
   if (c0 >= len || c1 <= kstart) {
@@ -397,12 +400,13 @@ template <int D>
 static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_parts, long long qkv_part_stride,
                             const float *table, int table_rows, int rot_dim,
                             const int *tok_pos, const int *page_table, int pt_stride, void *kc, void *vc,
-                            int write_cache, int n_seqs, int n_heads, int n_kv, int chunk, int n_splits, int window,
-                            float scale, float *ws_o, float *ws_ml, int *counters, void *out, long long out_stride,
+                            int write_cache, int n_seqs, int n_heads, int n_kv, int chunk, int max_len, int n_splits,
+                            int window, float scale, float *ws_o, float *ws_ml, int *counters, void *out, long long out_stride,
                             cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t tiles = (size_t)(DT_ROWS + 2 + 2 * decode_tc_stages(D) * DT_BN) * LD * sizeof(__nv_bfloat16);
-  const size_t smem = tiles + (size_t)(chunk / DT_BN + 2) * sizeof(int);
+  const int widest = chunk > 0 ? chunk : ((max_len + n_splits - 1) / n_splits + 2 * DT_BN);
+  const size_t smem = tiles + (size_t)(widest / DT_BN + 2) * sizeof(int);
   LLM_REQUIRE(smem <= 200 * 1024, "attention_decode_tc: a chunk of %d keys spans too many pages", chunk);
   constexpr int DT_WARPS = 4;
   auto kern = attention_decode_tc_kernel<D, DT_WARPS>;
@@ -436,14 +440,17 @@ LLM_EXPORT int llm_attention_decode_tc_supports(int d, int page_size, int group)
 // qkv [B, (heads + 2 kv_heads) * d] 32-bit (the stacked product, not rotated; with qkv_parts > 1 it
 // is the sum of that many partial products qkv_part_stride floats apart), table
 // [positions, rot_dim] (cosines, then sines), caches [pages, kv_heads, 64, d] bfloat16, tok_pos[b]
-// the position of sequence b's token.  With write_cache the token's k and v are appended.
+// the position of sequence b's token.  With write_cache the token's k and v are appended.  Keys are
+// cut into n_splits runs of `chunk`, or, with chunk 0, each sequence's own length into n_splits runs of
+// whole pages (max_len then bounds the lengths: it sizes the CTA's list of pages).
 // ws_o needs B*heads*n_splits*d floats, ws_ml B*heads*n_splits*2, counters B*kv_heads ints that are
 // zero before the first launch (the kernel leaves them zero).
 LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, int qkv_parts,
                                        long long qkv_part_stride, const float *table, int table_rows,
                                        int rot_dim, const int *tok_pos, const int *page_table, int pt_stride,
                                        void *kc, void *vc, int write_cache, int n_seqs, int n_heads, int n_kv, int d,
-                                       int page_size, int chunk, int n_splits, int window, float scale, float *ws_o,
+                                       int page_size, int chunk, int max_len, int n_splits, int window, float scale,
+                                       float *ws_o,
                                        float *ws_ml, int *counters, void *out, long long out_stride,
                                        cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
@@ -452,8 +459,9 @@ LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, i
   LLM_REQUIRE(llm_attention_decode_tc_supports(d, page_size, n_heads / n_kv),
               "attention_decode_tc: head size %d, pages of %d, %d query heads per kv head is not built", d, page_size,
               n_heads / n_kv);
-  LLM_REQUIRE(chunk > 0 && chunk % page_size == 0 && n_splits >= 1,
-              "attention_decode_tc: chunk %d must be a positive multiple of the page size", chunk);
+  LLM_REQUIRE(chunk >= 0 && chunk % page_size == 0 && n_splits >= 1 && (chunk > 0 || max_len > 0),
+              "attention_decode_tc: chunk %d must be a multiple of the page size (0: cut each sequence's own length, "
+              "then a bound on the lengths is needed)", chunk);
   LLM_REQUIRE(rot_dim > 0 && rot_dim % 2 == 0 && rot_dim <= d, "attention_decode_tc: rotated width %d does not fit head size %d", rot_dim, d);
   LLM_REQUIRE(n_splits == 1 || (ws_o && ws_ml && counters), "attention_decode_tc: splits need scratch memory");
   LLM_REQUIRE(qkv_parts >= 1 && qkv_parts <= 64, "attention_decode_tc: %d parts of the stacked product", qkv_parts);
@@ -462,7 +470,8 @@ LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, i
 #define DT_CASE(DD)                                                                                                 \
   if (d == DD)                                                                                                      \
     return launch_decode_tc<DD>(qkv, qkv_stride, qkv_parts, qkv_part_stride, table, table_rows, rot_dim, tok_pos, page_table, pt_stride, kc, vc, \
-                                write_cache, n_seqs, n_heads, n_kv, chunk, n_splits, window, scale, ws_o, ws_ml,    \
+                                write_cache, n_seqs, n_heads, n_kv, chunk, max_len, n_splits, window, scale, ws_o,  \
+                                ws_ml,                                                                              \
                                 counters, out, out_stride, stream);
   DT_CASE(16) DT_CASE(32) DT_CASE(48) DT_CASE(64) DT_CASE(80) DT_CASE(96) DT_CASE(112) DT_CASE(128)
 #undef DT_CASE

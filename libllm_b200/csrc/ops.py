@@ -385,11 +385,13 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
                         vcache: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int,
                         n_kv: int, head_dim: int, page_size: int, chunk: int, n_splits: int, window: Optional[int],
                         scale: float, write_cache: bool, ws_o: Optional[torch.Tensor],
-                        ws_ml: Optional[torch.Tensor], counters: Optional[torch.Tensor]) -> torch.Tensor:
+                        ws_ml: Optional[torch.Tensor], counters: Optional[torch.Tensor],
+                        max_len: int = 0) -> torch.Tensor:
     """One token per sequence: rotates q and k of the 32-bit stacked rows ``qkv``, appends k and v to
     the cache (with ``write_cache``), attends over the cache and joins the key splits, in one launch.
     ``counters`` (int32, one per sequence and kv head) must be zero before the first launch; the
-    kernel leaves it zero."""
+    kernel leaves it zero.  ``chunk`` 0 cuts each sequence's own length into ``n_splits`` runs; ``max_len``
+    then bounds the lengths."""
     _on_gpu(qkv, out, table, kcache, vcache, tok_pos, page_table, ws_o, ws_ml, counters)
     parts, part_stride = 1, 0
     if qkv.dim() == 3:                       # [parts, B, W]: partial products over K, added in the kernel
@@ -410,11 +412,11 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
         assert counters.dtype == torch.int32 and counters.numel() >= B * n_kv
     _call("attention_decode_tc", "llm_attention_decode_tc",
           [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
            c_void_p, c_void_p, c_longlong, c_void_p],
           _ptr(qkv), qkv2.stride(0) if B > 1 else qkv2.shape[1], parts, part_stride, _ptr(table), table.shape[0],
           table.shape[1],
           _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache), 1 if write_cache else 0,
-          B, n_heads, n_kv, head_dim, page_size, chunk, n_splits, int(window or 0), float(scale), _ptr(ws_o),
-          _ptr(ws_ml), _ptr(counters), _ptr(out), out.stride(0) if B > 1 else out.shape[1], _stream())
+          B, n_heads, n_kv, head_dim, page_size, chunk, int(max_len), n_splits, int(window or 0), float(scale),
+          _ptr(ws_o), _ptr(ws_ml), _ptr(counters), _ptr(out), out.stride(0) if B > 1 else out.shape[1], _stream())
     return out

@@ -98,18 +98,14 @@ def fused_decode_possible(ctx, cache, spec) -> bool:
                 and ops.attention_decode_tc_supported(spec.head_dim, cache.page_size, group))
 
 
-def fused_decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, head_dim: int = 64) -> Tuple[int, int]:
-    """(chunk, n_splits) for the fused decode attention: as many key splits as fill the GPU once
-    (all CTAs resident together: no second, partly filled wave), each of at least one page; like
-    ``decode_split`` it depends on the graph's bound on the length, not on the lengths themselves."""
+def fused_decode_splits(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int, head_dim: int = 64) -> int:
+    """Key splits per sequence for the fused decode attention: as many as fill the GPU once (all
+    CTAs resident together: no second, partly filled wave), each of at least a page at the longest
+    length.  The kernel cuts every sequence's own length into that many runs, so the number
+    depends on the batch and on the graph's bound on the length, not on the lengths themselves."""
     pairs = max(1, n_seqs * n_kv)
     slots = SM_COUNT * ops.attention_decode_tc_ctas_per_sm(head_dim)
-    want = max(1, slots // pairs)
-    most = max(1, max_kv_len // page_size)
-    n_splits = max(1, min(want, most))
-    chunk = (max_kv_len + n_splits - 1) // n_splits
-    chunk = (chunk + page_size - 1) // page_size * page_size
-    return chunk, max(1, (max_kv_len + chunk - 1) // chunk)
+    return max(1, min(slots // pairs, max(1, max_kv_len // page_size)))
 
 
 def fused_decode_attention(ctx, qkv: torch.Tensor, cache, spec, table: torch.Tensor,
@@ -119,8 +115,8 @@ def fused_decode_attention(ctx, qkv: torch.Tensor, cache, spec, table: torch.Ten
     stacked product, [T, W] or [parts, T, W]."""
     if not fused_decode_possible(ctx, cache, spec) or qkv.dtype != torch.float32:
         return None
-    chunk, n_splits = fused_decode_split(ctx.n_seqs, spec.n_kv_heads, max(ctx.max_kv_len, 1), cache.page_size,
-                                         spec.head_dim)
+    max_len = max(ctx.max_kv_len, 1)
+    n_splits = fused_decode_splits(ctx.n_seqs, spec.n_kv_heads, max_len, cache.page_size, spec.head_dim)
     dev = qkv.device
     out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=torch.bfloat16, device=dev)
     ws_o = ws_ml = counters = None
@@ -129,8 +125,8 @@ def fused_decode_attention(ctx, qkv: torch.Tensor, cache, spec, table: torch.Ten
         ws_ml = torch.empty(ctx.n_seqs * spec.n_heads * n_splits * 2, dtype=torch.float32, device=dev)
         counters = _zero_counters(dev, ctx.n_seqs * spec.n_kv_heads)
     return ops.attention_decode_tc(qkv, out, table, cache.k, cache.v, ctx.tok_pos, cache.page_table, spec.n_heads,
-                                   spec.n_kv_heads, spec.head_dim, cache.page_size, chunk, n_splits, spec.window,
-                                   scale, cache.writes, ws_o, ws_ml, counters)
+                                   spec.n_kv_heads, spec.head_dim, cache.page_size, 0, n_splits, spec.window,
+                                   scale, cache.writes, ws_o, ws_ml, counters, max_len=max_len)
 
 
 def attention(ctx, q: torch.Tensor, cache, spec, scale: float) -> Optional[torch.Tensor]:

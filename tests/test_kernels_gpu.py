@@ -466,7 +466,7 @@ def test_tensor_core_product_rows_do_not_depend_on_the_batch():
 
 @pytest.mark.parametrize("n_heads,n_kv,d,window", [(4, 2, 16, None), (3, 1, 32, None), (32, 8, 64, None), (8, 1, 128, None),
                                                      (8, 8, 64, None), (6, 2, 128, 100), (10, 2, 48, None)])
-@pytest.mark.parametrize("chunk,n_splits", [(64, 16), (192, 6), (1024, 1)])
+@pytest.mark.parametrize("chunk,n_splits", [(64, 16), (192, 6), (1024, 1), (0, 5)])     # 0: each length cut into 5 runs
 def test_attention_decode_fused(n_heads, n_kv, d, window, chunk, n_splits):
     """Rotation, cache append, attention and the joining of splits in one launch: the outputs
     against the plain rotation + attention, the cache rows it must have written, and a second
@@ -496,7 +496,7 @@ def test_attention_decode_fused(n_heads, n_kv, d, window, chunk, n_splits):
         tok_pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
         assert ops.attention_decode_tc_supported(d, page, n_heads // n_kv)
         ops.attention_decode_tc(qkv_in, out, table, K, V, tok_pos, table_pt, n_heads, n_kv, d, page, chunk, n_splits, window,
-                                1 / math.sqrt(d), True, ws_o, ws_ml, counters)
+                                1 / math.sqrt(d), True, ws_o, ws_ml, counters, max_len=1100)
         assert int(counters.abs().sum()) == 0
         x = qkv.cpu().view(B, n_heads + 2 * n_kv, d)
         for b in range(B):
