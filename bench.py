@@ -33,6 +33,12 @@ LLAMA_1B = dict(model_type="llama", num_hidden_layers=16, hidden_size=2048, num_
                                   original_max_position_embeddings=8192),
                 rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072,
                 hidden_act="silu")
+LLAMA_3B = dict(LLAMA_1B, num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8,
+                head_dim=128, intermediate_size=8192)
+LLAMA_8B = dict(LLAMA_1B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192))
 CONTEXT = 4096
 PROMPT = 2048
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
@@ -201,6 +207,63 @@ def prefill_rate(model, vocab, flops_fn, peak_tflops, reps=3):
     return dict(value=PROMPT * 1000.0 / ms, tokens=PROMPT, ms=ms, frac=flops / (ms * 1e-3) / (peak_tflops * 1e12))
 
 
+def run_workload(args):
+    """The two larger workloads the benchmark description names, through Model.generate (host token ids in
+    and out): Llama-3.2-3B sizes with 16 prompts of lengths uniform in [128, 2048] and 256 decoded tokens
+    each; Llama-3.1-8B sizes with 32 prompts of 4,096 tokens and 512 decoded tokens each.  One JSON line:
+    time to the first tokens (all prompts in one step), decoded tokens a second after it, and the bytes
+    the decode steps had to read against the memory bandwidth."""
+    import torch
+    from libllm_b200 import Model
+    if args.workload == "3b":
+        cfg, n_new = dict(LLAMA_3B), 256
+        g = torch.Generator().manual_seed(11)
+        lens = torch.randint(128, 2049, (16,), generator=g).tolist()
+        context = 2048 + n_new
+    else:
+        cfg, n_new = dict(LLAMA_8B), 512
+        lens = [4096] * 32
+        context = 8192
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    pages = sum((n + n_new + 63) // 64 for n in lens)
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=pages * 64, max_seq_len=context)
+    stamps = []
+
+    def on_token(i, tok):
+        if i == 0:
+            stamps.append(time.perf_counter())
+
+    model.generate(prompts[:2], max_new_tokens=4, temperature=0.0, stop_token_ids=[])        # kernels loaded, graphs not
+    t0 = time.perf_counter()
+    out = model.generate(prompts, max_new_tokens=n_new, temperature=0.0, stop_token_ids=[], max_batch=len(prompts),
+                         on_token=on_token)
+    t1 = time.perf_counter()
+    assert all(len(o) == n_new for o in out)
+    wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+    pk = peaks()
+    ttft = stamps[0] - t0
+    decode_s = t1 - stamps[0]
+    steps = n_new - 1
+    mean_ctx = sum(lens) / len(lens) + n_new / 2
+    step_bytes = wbytes + len(lens) * mean_ctx * kv_per_tok
+    prefill_flops = sum(flops_fn(n) for n in lens)
+    print(json.dumps({
+        "workload": args.workload, "impl": "ours", "dtype": "bf16", "data": "synthetic",
+        "config": {"layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "batch": len(lens),
+                   "prompt_tokens": sum(lens), "new_tokens_each": n_new},
+        "prefill": {"tokens": sum(lens), "ms": round(ttft * 1e3, 2), "tok_s": round(sum(lens) / ttft, 1),
+                    "frac": round(prefill_flops / ttft / (pk["bf16_tflops"] * 1e12), 4)},
+        "decode": {"tok_s": round(len(lens) * steps / decode_s, 1), "ms_per_step": round(decode_s / steps * 1e3, 3),
+                   "hbm_frac": round(step_bytes / (decode_s / steps) / 1e9 / pk["hbm_gbs"], 4)},
+        "total_s": round(t1 - t0, 3)}))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "ling0322/libllm's root is not pip-installable; its python/ folder installs only a ctypes "
@@ -219,6 +282,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--workload", choices=["1b", "3b", "8b"], default="1b",
+                    help="1b: the benchmark line (default); 3b, 8b: the larger workloads, a line of their own")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling; not a bench record)")
     args = ap.parse_args()
@@ -228,6 +293,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload != "1b":
+        return run_workload(args)
 
     import torch
     from libllm_b200 import Model
