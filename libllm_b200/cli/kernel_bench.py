@@ -191,14 +191,17 @@ def bench_attention_prefill(args, timer):
     seq_past = torch.zeros(B, device="cuda", dtype=torch.int32)
     scale = 1.0 / math.sqrt(d)
     use_fast = not args.generic and ops.attention_prefill_supported(d, 64)
+    use_tc = use_fast and not args.mma_sync and ops.attention_prefill_tc_supported(d, 64)
 
     def fn():
-        if use_fast:
+        if use_tc:
+            ops.attention_prefill_tc(q, out, k, v, seq_start, seq_past, table, B, T, nH, nKV, d, 64, None, scale)
+        elif use_fast:
             ops.attention_prefill(q, out, k, v, seq_start, seq_past, table, B, T, nH, nKV, d, 64, None, scale)
         else:
             ops.attention_generic(q, out, k, v, tok_seq, tok_pos, table, nH, nKV, d, 64, None, scale)
     us = timer.run(fn)
-    report("attention_prefill" if use_fast else "attention_generic", us,
+    report("attention_prefill_tc" if use_tc else ("attention_prefill" if use_fast else "attention_generic"), us,
            flops=4 * B * nH * d * T * (T + 1) // 2, batch=B, tokens=T, heads=nH, kv_heads=nKV, head_dim=d)
 
 
@@ -262,6 +265,7 @@ def main(argv=None) -> int:
     ap.add_argument("--library", action="store_true", help="gemv, layer_products: time the library product instead")
     ap.add_argument("--separate", action="store_true",
                     help="attention_decode: time the FMA kernel with its join kernel instead of the fused one")
+    ap.add_argument("--mma-sync", action="store_true", help="attention_prefill: time the mma.sync kernel")
     ap.add_argument("--generic", action="store_true", help="attention_prefill: time the general kernel")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

@@ -29,106 +29,15 @@
 // frees its tensor memory and returns.  Weights are loaded before the programmatic dependency on
 // the previous kernel is waited for, tokens after it.
 #include "common.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tc_common.cuh"
 
 LLM_DEFINE_LAST_ERROR(llm_gemm_tc_last_error)
 
 namespace {
 
 constexpr int TC_THREADS = 192;
-constexpr int TC_BK = 64;                      // k per stage: 128 bytes, one swizzle row
 constexpr int TC_ROWS = 128;                   // rows of W per tile (UMMA M)
 constexpr int TC_A_BYTES = TC_ROWS * TC_BK * 2;
-constexpr unsigned long long TC_WAIT_NS = 2000000000ull;   // 2 s
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Waits for the barrier's phase with a time limit.  Returns false when the limit ran out or
-// another warp has given up (`*abort_flag` set); the first to give up records `code`.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, int *status,
-                                          int code) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer();
-  for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return mbar_try(bar, parity);
-    if (globaltimer() - t0 > TC_WAIT_NS) {
-      *abort_flag = 1;
-      if (status) atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                       unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
-  unsigned r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle, groups of
-// 8 rows 1024 bytes apart.  Fields: start address >> 4 (bits 0-13), leading offset (16-29, unused
-// for this layout), stride offset >> 4 (32-45), version 1 (46-47), swizzle mode 2 = 128 B (61-63).
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
-  d |= 1ull << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-// Instruction descriptor of kind::f16: D in 32-bit floats (bits 4-5 = 1), A and B bfloat16 (bits 7-9
-// and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr unsigned instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
 
 // SW: 0 plain product; 1 SwiGLU with gate and up rows interleaved in one 128-row tile (64 + 64,
 // handed over between epilogue warps: steps of few tokens, where a tile per SM matters); 2 SwiGLU with
@@ -399,83 +308,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
                  : "memory");
   }
-}
-
-// ---------------------------------------------------------------- tensor maps (host)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void *ptr;
-  long long rows, cols, ld;
-  int box_rows;
-  bool operator==(const MapKey &o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey &k) const {
-    size_t h = (size_t)k.ptr;
-    h = h * 1000003u ^ (size_t)k.rows;
-    h = h * 1000003u ^ (size_t)k.cols;
-    h = h * 1000003u ^ (size_t)k.ld;
-    return h * 1000003u ^ (size_t)k.box_rows;
-  }
-};
-
-// A map over a row-major bfloat16 matrix [rows, cols] with row stride ld (elements): boxes of
-// [box_rows x 64] elements, 128-byte swizzle, zeros outside.  Maps are kept: weights come back
-// with every step, and a captured step's activations keep their addresses.
-int get_map(const void *ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap *out) {
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  static std::mutex mu;
-  const MapKey key{ptr, rows, cols, ld, box_rows};
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) {
-    *out = it->second;
-    return LLM_OK;
-  }
-  EncodeTiledFn fn = encode_fn();
-  LLM_REQUIRE(fn != nullptr, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  CUtensorMap m;
-  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  LLM_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed (%d) for a [%lld x %lld] matrix", (int)r, rows, cols);
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, m);
-  *out = m;
-  return LLM_OK;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
 }
 
 template <int TN, int SW, typename TO>

@@ -420,3 +420,30 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
           B, n_heads, n_kv, head_dim, page_size, chunk, int(max_len), n_splits, int(window or 0), float(scale),
           _ptr(ws_o), _ptr(ws_ml), _ptr(counters), _ptr(out), out.stride(0) if B > 1 else out.shape[1], _stream())
     return out
+
+
+# ------------------------------------------------------------------ attention for prompts on tcgen05 (bfloat16)
+def attention_prefill_tc_supported(head_dim: int, page_size: int) -> bool:
+    lib = build.load("attention_prefill_tc")
+    f = lib.llm_attention_prefill_tc_supports
+    f.argtypes, f.restype = [c_int, c_int], c_int
+    return bool(f(head_dim, page_size))
+
+
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                         seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
+                         max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+                         window: Optional[int], scale: float) -> torch.Tensor:
+    """The same attention as ``attention_prefill`` with both products on tcgen05 (head sizes 64, 128)."""
+    _on_gpu(q, out, kcache, vcache, seq_start, seq_past, page_table)
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == q.shape[0]
+    assert seq_start.dtype == torch.int32 and seq_past.dtype == torch.int32 and page_table.dtype == torch.int32
+    assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
+    _call("attention_prefill_tc", "llm_attention_prefill_tc",
+          [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+          _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
+          _ptr(seq_start), _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv,
+          head_dim, page_size, int(window or 0), float(scale), _ptr(tc_status(q.device)), _stream())
+    return out

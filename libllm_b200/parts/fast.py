@@ -15,6 +15,7 @@ ENABLED = {
     "decode_attention": os.environ.get("LIBLLM_B200_NO_DECODE_ATTENTION") is None,
     "prefill_attention": os.environ.get("LIBLLM_B200_NO_PREFILL_ATTENTION") is None,
     "gemm_tc": os.environ.get("LIBLLM_B200_NO_GEMM_TC") is None,
+    "prefill_attention_tc": os.environ.get("LIBLLM_B200_NO_PREFILL_ATTENTION_TC") is None,
     "decode_attention_tc": os.environ.get("LIBLLM_B200_NO_DECODE_ATTENTION_TC") is None,
 }
 PRODUCT = os.environ.get("LIBLLM_B200_PRODUCT", "tc")           # "gemv": never the tcgen05 kernel
@@ -144,6 +145,11 @@ def attention(ctx, q: torch.Tensor, cache, spec, scale: float) -> Optional[torch
         return ops.attention_decode(q, out, cache.k, cache.v, ctx.tok_pos, cache.page_table, spec.n_heads,
                                     spec.n_kv_heads, spec.head_dim, cache.page_size, chunk, n_splits, spec.window,
                                     scale, ws_o, ws_ml)
+    if ENABLED["prefill_attention_tc"] and ops.attention_prefill_tc_supported(spec.head_dim, cache.page_size):
+        out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=q.dtype, device=q.device)
+        return ops.attention_prefill_tc(q, out, cache.k, cache.v, ctx.seq_start, ctx.seq_past, cache.page_table,
+                                        ctx.n_seqs, ctx.max_q_len, spec.n_heads, spec.n_kv_heads, spec.head_dim,
+                                        cache.page_size, spec.window, scale)
     if ENABLED["prefill_attention"] and ops.attention_prefill_supported(spec.head_dim, cache.page_size):
         out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=q.dtype, device=q.device)
         return ops.attention_prefill(q, out, cache.k, cache.v, ctx.seq_start, ctx.seq_past, cache.page_table,

@@ -514,3 +514,48 @@ def test_attention_decode_fused(n_heads, n_kv, d, window, chunk, n_splits):
             ref = P.attention_scores_softmax_values(q, ks[b][:pos[b] + 1], vs[b][:pos[b] + 1], window)
             # bfloat16 rounds relative to the value: a sequence of one or two keys returns values of up to 4
             close(out[b].view(1, n_heads, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d,window", [(32, 8, 64, None), (3, 1, 64, None), (8, 2, 128, None), (2, 2, 64, 64),
+                                                     (6, 3, 128, 130), (4, 1, 64, 37)])
+def test_attention_prefill_on_tcgen05(n_heads, n_kv, d, window):
+    """The tcgen05 kernel on the cases of the mma.sync one: whole prompts, the end of a prompt behind
+    cached tokens, tile edges (127, 128, 129 rows), single tokens, windows."""
+    from libllm_b200.csrc import ops
+    page = 64
+    lens = [1, 70, 333, 200, 128, 129, 127, 300]
+    q_lens = [1, 70, 5, 150, 128, 129, 1, 300]
+    B = len(lens)
+    K, V, table, ks, vs = paged_cache(B, lens, n_kv, d, page, "bfloat16", 71)
+    T = sum(q_lens)
+    q = rnd((T, n_heads * d), "bfloat16", 72)
+    out = torch.full((T, n_heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    start, past = prefill_inputs(lens, q_lens)
+    assert ops.attention_prefill_tc_supported(d, page)
+    ops.attention_prefill_tc(q, out, K, V, start, past, table, B, max(q_lens), n_heads, n_kv, d, page, window,
+                             1 / math.sqrt(d))
+    ops.check_tc_status()
+    o = 0
+    for s, n in enumerate(q_lens):
+        ref = P.attention_scores_softmax_values(q[o:o + n].cpu().view(n, n_heads, d), ks[s], vs[s], window)
+        close(out[o:o + n].view(n, n_heads, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
+        o += n
+
+
+def test_attention_prefill_on_tcgen05_finds_a_far_key_and_respects_the_window_edge():
+    from libllm_b200.csrc import ops
+    d, page, L = 64, 64, 900
+    K, V, table, ks, vs = paged_cache(1, [L], 1, d, page, "bfloat16", 73)
+    q = rnd((L, d), "bfloat16", 74)
+    k3 = (q[700].float().cpu() * 3.0).to(torch.bfloat16)
+    K[int(table[0, 0]), 0, 3] = k3.to(DEV)
+    ks[0][3, 0] = k3
+    start, past = prefill_inputs([L], [L])
+    for window, sees in ((None, True), (697, False), (698, True)):
+        out = torch.empty((L, d), dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, 1, 1, d, page, window, 1 / math.sqrt(d))
+        ops.check_tc_status()
+        ref = P.attention_scores_softmax_values(q.cpu().view(L, 1, d), ks[0], vs[0], window)
+        close(out.view(L, 1, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
+        near = float((out[700].float().cpu() - vs[0][3, 0].float()).abs().max()) < 0.2
+        assert near == sees, (window, near)
