@@ -410,9 +410,7 @@ static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_part
   LLM_REQUIRE(smem <= 200 * 1024, "attention_decode_tc: a chunk of %d keys spans too many pages", chunk);
   constexpr int DT_WARPS = 4;
   auto kern = attention_decode_tc_kernel<D, DT_WARPS>;
-  if (smem > 48 * 1024)
-    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                   "attention_decode_tc attribute");
+  LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "attention_decode_tc attribute");
   dim3 grid(n_splits, n_kv, n_seqs);
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(DT_WARPS * 32), smem, stream, qkv, qkv_stride, qkv_parts, qkv_part_stride, table, table_rows,
                             rot_dim,

@@ -222,9 +222,7 @@ static int launch_prefill(const void *q, long long q_stride, void *out, long lon
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(AP_BM + 4 * AP_BN) * LD * sizeof(__nv_bfloat16);
   auto kern = attention_prefill_kernel<D>;
-  if (smem > 48 * 1024)
-    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                   "attention_prefill attribute");
+  LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "attention_prefill attribute");
   dim3 grid((max_q_len + AP_BM - 1) / AP_BM, n_heads, n_seqs);
   llm_launch(kern, grid, dim3(AP_WARPS * 32), smem, stream, (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out,
              out_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, seq_start, seq_past, page_table,

@@ -313,12 +313,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   rc = get_map(vc, n_pages * n_kv * FT_BN, D, D, 64, &map_v);
   if (rc != LLM_OK) return rc;
   auto kern = attention_prefill_tc_kernel<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM),
-                   "attention_prefill_tc attribute");
-    attr_set = true;
-  }
+  LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "attention_prefill_tc attribute");
   dim3 grid((max_q_len + FT_BM - 1) / FT_BM, n_heads, n_seqs);
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FT_THREADS), S::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
                             out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window,

@@ -72,22 +72,32 @@ static inline bool llm_pdl_enabled() {
   return on;
 }
 
-// Every kernel of a step asks for the same split of an SM's on-chip memory (all of it as shared
-// memory): kernels that overlap under programmatic dependent launch then never make an SM wait
-// until it is empty to change the split.
+// Dynamic shared memory above 48 KB has to be allowed per kernel; the attribute is set when a
+// kernel first needs more than it has been allowed so far (a launch outside any stream capture: a
+// step runs once before it is captured), never on every launch.
 template <typename... KArgs>
-static inline void llm_same_carveout(void (*kernel)(KArgs...)) {
-  static thread_local const void *last = nullptr;
-  if (last == (const void *)kernel) return;
-  last = (const void *)kernel;
-  static const bool on = getenv("LIBLLM_B200_NO_CARVEOUT") == nullptr;
-  if (on) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+static inline cudaError_t llm_allow_smem(void (*kernel)(KArgs...), size_t smem) {
+  static thread_local const void *seen[64];
+  static thread_local size_t allowed[64];
+  static thread_local int n_seen = 0;
+  if (smem <= 48 * 1024) return cudaSuccess;
+  int i = 0;
+  for (; i < n_seen; ++i)
+    if (seen[i] == (const void *)kernel) break;
+  if (i < n_seen && allowed[i] >= smem) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  if (i == n_seen && n_seen < 64) {
+    seen[n_seen] = (const void *)kernel;
+    ++n_seen;
+  }
+  if (i < 64) allowed[i] = smem;
+  return cudaSuccess;
 }
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t llm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                      cudaStream_t stream, Args... args) {
-  llm_same_carveout(kernel);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

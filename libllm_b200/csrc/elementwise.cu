@@ -175,8 +175,7 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
   auto kern = add_rmsnorm_kernel<TD, TO, THREADS>;
   if (smem > 48 * 1024) {
     LLM_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: a row of %d values does not fit shared memory", hidden);
-    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                   "add_rmsnorm attribute");
+    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "add_rmsnorm attribute");
   }
   llm_launch(kern, n_rows, THREADS, smem, stream, resid, (const TD *)delta, n_parts, part_stride, weight, eps,
              (TO *)out, rows, hidden);

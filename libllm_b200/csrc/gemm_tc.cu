@@ -327,11 +327,7 @@ int launch_tc(const void *x, long long ldx, const void *W, void *out, long long 
   rc = get_map(x, M, K, ldx, TN, &map_x);
   if (rc != LLM_OK) return rc;
   auto kern = gemm_tc_kernel<TN, SW, TO>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM), "gemm_tc attribute");
-    attr_set = true;
-  }
+  LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "gemm_tc attribute");
   const long long tiles = (long long)row_tiles * tok_tiles * k_parts;
   LLM_REQUIRE(tiles < (1ll << 30), "gemm_tc: too many tiles");
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());

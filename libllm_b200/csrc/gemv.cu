@@ -208,8 +208,7 @@ static int launch_gemv(const void *x, long long ldx, const void *W, void *out, l
   const int grid = (n_out + rows_per_cta - 1) / rows_per_cta;
   const size_t smem = k_split > 1 ? (size_t)GEMV_WARPS * SETS * MT * NT * 4 * 32 * sizeof(float) : 0;
   auto kern = gemv_kernel<NT, MT, UNROLL, SWIGLU, TO>;
-  if (smem > 48 * 1024)
-    LLM_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv attribute");
+  LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "gemv attribute");
   llm_launch(kern, dim3(grid, k_parts), dim3(GEMV_WARPS * 32), smem, stream, (const __nv_bfloat16 *)x, ldx,
              (const __nv_bfloat16 *)W, (TO *)out, ldo, M, N, K, k_split, kb_per_part, part_stride);
   LLM_CHECK_LAUNCH("gemv");

@@ -13,6 +13,7 @@ CUDA graph and replayed; the step's descriptor (tokens, positions, page tables) 
 copied into the graph's fixed buffer before each replay."""
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -421,8 +422,19 @@ class _DecodeGraph:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self._static = self._body()
+            # Nothing but the step's own launches may happen while it is captured.  Python's
+            # garbage collector could otherwise pick this moment to destroy CUDA objects of an
+            # engine dropped earlier (graphs, events, pinned buffers), and a call such as a free
+            # from a destructor invalidates the capture.
+            gc_was_on = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+                    self._static = self._body()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.logits, self.tokens = logits, tokens
             return
         self.graph.replay()

@@ -9,6 +9,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..csrc import ops
+from ..errors import UnsupportedError
 
 ENABLED = {
     "gemv": os.environ.get("LIBLLM_B200_NO_GEMV") is None,
@@ -85,11 +86,18 @@ def decode_split(n_seqs: int, n_kv: int, max_kv_len: int, page_size: int) -> Tup
 _counters = {}
 
 
+COUNTERS = 1 << 18
+
+
 def _zero_counters(device, n: int) -> torch.Tensor:
-    """int32 zeros that the fused decode attention counts finished splits in (and leaves zero)."""
+    """int32 zeros in which the fused decode attention counts finished splits (it leaves them zero).
+    One buffer per device for good: captured steps keep its address."""
+    if n > COUNTERS:
+        raise UnsupportedError(f"fused decode attention: {n} (sequence, kv head) pairs in one step, "
+                               f"{COUNTERS} are provided for")
     t = _counters.get(device)
-    if t is None or t.numel() < n:
-        t = _counters[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    if t is None:
+        t = _counters[device] = torch.zeros(COUNTERS, dtype=torch.int32, device=device)
     return t
 
 
