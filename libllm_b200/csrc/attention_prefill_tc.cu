@@ -3,12 +3,12 @@
 // tcgen05.mma, their accumulators in tensor memory and all operands brought by TMA.
 //
 // One CTA takes 128 query rows of one head of one sequence.  Its warps:
-//   warp 0    one lane loads the Q tile once and then, page by page, the K and V tiles (a page of
+//   warp 4    one lane loads the Q tile once and then, page by page, the K and V tiles (a page of
 //             the cache is a [64, d] block = one key tile) into a ring of shared-memory stages;
-//   warp 1    one lane issues S = Q K^T (operands K-major, 128-byte swizzle) into tensor memory and,
+//   warp 5    one lane issues S = Q K^T (operands K-major, 128-byte swizzle) into tensor memory and,
 //             when the probabilities are ready, O_j = P V_j (V is the MN-major operand: it lies
 //             [key][channel] in the cache and is used as it is) into a second accumulator;
-//   warps 2-5 a thread per query row: reads its row of S from tensor memory (no shuffles: the row is
+//   warps 0-3 a thread per query row: reads its row of S from tensor memory (no shuffles: the row is
 //             one lane), masks, keeps the running maximum and sum in 32-bit, writes the row of P as
 //             bfloat16 into shared memory in the swizzled layout the tensor core reads, then adds
 //             O_j to its output row scaled by exp(old maximum - new maximum).
@@ -29,7 +29,7 @@ LLM_DEFINE_LAST_ERROR(llm_attention_prefill_tc_last_error)
 
 namespace {
 
-constexpr int FT_THREADS = 192;
+constexpr int FT_THREADS = 256;   // warps 0-3: a thread per query row; 4: loader; 5: tensor-core issue; 6, 7: none
 constexpr int FT_BM = 128;          // query rows per CTA
 constexpr int FT_BN = 64;           // keys per tile = tokens per page
 
@@ -40,8 +40,11 @@ struct FtShape {
   static constexpr int KV_BYTES = FT_BN * D * 2;            // one of K or V
   static constexpr int P_BYTES = FT_BM * FT_BN * 2;
   static constexpr int STAGES = D == 64 ? 4 : 2;
-  static constexpr int TMEM_COLS = D == 64 ? 128 : 256;     // S (64 columns) + O_j (D columns), a power of two
-  static constexpr size_t SMEM = 1024 + Q_BYTES + P_BYTES + (size_t)STAGES * 2 * KV_BYTES + 256;
+  static constexpr int TMEM_COLS = 256;                     // two S buffers (64 columns each) + O_j (D columns)
+  static constexpr size_t SMEM = Q_BYTES + P_BYTES + (size_t)STAGES * 2 * KV_BYTES + 256;   // two CTAs per SM
+  // Registers move from the second warpgroup (loader, issuer) to the first (the row threads), which
+  // keep a row of the output and a row of scores each: 2 CTAs x 256 threads x 128 registers at launch.
+  static constexpr int REGS_FEW = 56, REGS_MANY = 256 - REGS_FEW;
 };
 
 
@@ -51,8 +54,15 @@ __device__ __forceinline__ unsigned long long smem_desc_mn(unsigned addr) { retu
 
 __host__ __device__ constexpr unsigned instr_desc_mn(int m, int n) { return instr_desc(m, n) | (1u << 16); }
 
+// exp2 of a number that is never above zero here: one instruction (inputs of -inf give 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
-__global__ void __launch_bounds__(FT_THREADS, D == 64 ? 2 : 1)
+__global__ void __launch_bounds__(FT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
                             long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
@@ -60,19 +70,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             float scale_log2, int *status) {
   using S = FtShape<D>;
   constexpr int STAGES = S::STAGES;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char *sQ = smem, *sP = smem + S::Q_BYTES, *sKV = sP + S::P_BYTES;
   unsigned long long *bars = (unsigned long long *)(sKV + (size_t)STAGES * 2 * S::KV_BYTES);
-  // full[STAGES], empty[STAGES], q_full, s_full, s_free, p_full, o_full, o_free
+  // full[STAGES], empty[STAGES], q_full, s_full[2] (one per score buffer), p_full, o_full, o_free
   const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
-  const unsigned bar_q = smem_u32(bars + 2 * STAGES), bar_sfull = bar_q + 8, bar_sfree = bar_q + 16,
+  const unsigned bar_q = smem_u32(bars + 2 * STAGES), bar_sfull = bar_q + 8,
                  bar_pfull = bar_q + 24, bar_ofull = bar_q + 32, bar_ofree = bar_q + 40;
   unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 6);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_dependents_launch();
+  if (smem_u32(smem) & 1023u) {                               // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(status, 0, 21);
+    return;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -80,14 +93,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     mbar_init(bar_q, 1);
     mbar_init(bar_sfull, 1);
-    mbar_init(bar_sfree, 4);
+    mbar_init(bar_sfull + 8, 1);
     mbar_init(bar_pfull, 4);
     mbar_init(bar_ofull, 1);
     mbar_init(bar_ofree, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((unsigned)S::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -96,7 +109,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  const unsigned tmem_s = tmem_base, tmem_o = tmem_base + FT_BN;
+  const unsigned tmem_s = tmem_base, tmem_o = tmem_base + 2 * FT_BN;
 
   // every thread: the previous kernel wrote the queries and this step's keys and values
   grid_dependency_wait();
@@ -112,7 +125,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int n_tiles = last_tile - first_tile + 1;             // <= 0: nothing to do
   const int *pt = page_table + (size_t)b * pt_stride;
 
-  if (warp == 0) {
+  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
+  if (warp == 4) {
     // ------------------------------------------------------------ loader
     if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(bar_q, S::Q_BYTES);
@@ -145,22 +159,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 5) {
     // ------------------------------------------------------------ tensor-core issue
     if (lane == 0 && n_tiles > 0) {
       constexpr unsigned IDESC_S = instr_desc(FT_BM, FT_BN);          // S[128 x 64 keys], both operands K-major
       constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, 64);          // O_j[128 x 64 channels], V MN-major
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
-      auto issue_s = [&](int j) {                                      // scores of tile j from its stage
+      auto issue_s = [&](int j) {                                      // scores of tile j into buffer j & 1
         const int stage = j % STAGES;
         const unsigned ka = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < S::KB; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tc_mma(tmem_s, smem_desc(smem_u32(sQ) + kb * (FT_BM * 128) + kk * 32),
+            tc_mma(tmem_s + (j & 1) * FT_BN, smem_desc(smem_u32(sQ) + kb * (FT_BM * 128) + kk * 32),
                    smem_desc(ka + kb * (FT_BN * 128) + kk * 32), IDESC_S, (kb > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(bar_sfull);
+        tc_commit(bar_sfull + 8 * (j & 1));
       };
       if (ok) ok = mbar_wait(bar_full, 0, abort_flag, status, 13);
       if (ok) {
@@ -169,10 +183,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) {
-          // the next tile's scores as soon as the row threads have taken this tile's out of tensor memory
+          // The next tile's scores go into the other buffer at once: its last reader was tile
+          // j - 1, whose probabilities this thread has already waited for.
           const int s1 = (j + 1) % STAGES;
-          ok = mbar_wait(bar_full + 8 * s1, ((j + 1) / STAGES) & 1, abort_flag, status, 14) &&
-               mbar_wait(bar_sfree, j & 1, abort_flag, status, 15);
+          ok = mbar_wait(bar_full + 8 * s1, ((j + 1) / STAGES) & 1, abort_flag, status, 14);
           if (!ok) break;
           tc_fence_after();
           issue_s(j + 1);
@@ -193,82 +207,141 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_commit(bar_empty + 8 * stage);
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ------------------------------------------------------------ a thread per query row
-    const int quarter = warp & 3;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(S::REGS_MANY));
+    const int quarter = warp;
     const int row = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
     const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
     const int pos = past + r0 + row;                           // the row's position in its sequence
     float o[D];
 #pragma unroll
     for (int c = 0; c < D; ++c) o[c] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
     bool ok = true;
+    // o = o * a + (the tile's product in tensor memory), OB * 16 channels with OB loads in flight
+    constexpr int OB = D == 64 ? 4 : 2;
+    auto add_output = [&](float a) {
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += OB * 16) {
+        float t[OB][16];
+#pragma unroll
+        for (int c = 0; c < OB; ++c) tc_ld16_issue(tmem_o + lane_addr + c0 + c * 16, t[c]);
+        tc_ld_wait();
+#pragma unroll
+        for (int c = 0; c < OB; ++c) tc_ld_ready(t[c]);
+#pragma unroll
+        for (int c = 0; c < OB; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[c0 + c * 16 + i] = fmaf(o[c0 + c * 16 + i], a, t[c][i]);
+      }
+    };
     for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull, j & 1, abort_flag, status, 18));
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, status, 18));
       if (!ok) break;
       tc_fence_after();
-      float s[FT_BN];
-#pragma unroll
-      for (int c0 = 0; c0 < FT_BN; c0 += 16) tc_ld16(tmem_s + lane_addr + c0, *reinterpret_cast<float(*)[16]>(&s[c0]));
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sfree);                   // the scores are in registers
+      const unsigned s_addr = tmem_s + (j & 1) * FT_BN + lane_addr;
       const int k0 = (first_tile + j) * FT_BN;
       const bool edge = (k0 + FT_BN - 1 > past + r0) || (window > 0 && k0 <= past + r0 + FT_BM - 1 - window);
-      if (edge) {
+      // The row's scores come into registers NB * 16 at a time, with NB loads in flight and one wait.
+      // A head size of 64 leaves room for the whole row (NB = 4), which is then read once; a larger
+      // one reads it twice, first for the maximum and then for the exponentials.
+      constexpr int NB = D == 64 ? 4 : 2;
+      auto load_scores = [&](int c0, float (&v)[NB][16]) {
 #pragma unroll
-        for (int c = 0; c < FT_BN; ++c) {
-          const int key = k0 + c;
-          if (!(key <= pos && (window <= 0 || key > pos - window))) s[c] = -INFINITY;
+        for (int c = 0; c < NB; ++c) tc_ld16_issue(s_addr + c0 + c * 16, v[c]);
+        tc_ld_wait();
+#pragma unroll
+        for (int c = 0; c < NB; ++c) tc_ld_ready(v[c]);
+        if (edge) {
+#pragma unroll
+          for (int c = 0; c < NB; ++c)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int key = k0 + c0 + c * 16 + i;
+              if (!(key <= pos && (window <= 0 || key > pos - window))) v[c][i] = -INFINITY;
+            }
         }
-      }
+      };
+      // exponentials of NB * 16 scores and their pieces of the row of P, 16 bytes (8 keys) at a time,
+      // where the tensor core expects it: row r lies at (r / 8) * 1024 + (r % 8) * 128, its 16-byte
+      // piece c at piece c ^ (r % 8)
+      unsigned char *prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+      float sum = 0.f;
+      auto write_p = [&](int c0, float (&v)[NB][16], float moff) {
+#pragma unroll
+        for (int c = 0; c < NB; ++c) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            v[c][i] = fast_exp2(fmaf(v[c][i], scale_log2, -moff));
+            sum += v[c][i];
+          }
+#pragma unroll
+          for (int h8 = 0; h8 < 2; ++h8) {
+            uint4 w;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[c][h8 * 8], v[c][h8 * 8 + 1]),
+                           t1 = __floats2bfloat162_rn(v[c][h8 * 8 + 2], v[c][h8 * 8 + 3]),
+                           t2 = __floats2bfloat162_rn(v[c][h8 * 8 + 4], v[c][h8 * 8 + 5]),
+                           t3 = __floats2bfloat162_rn(v[c][h8 * 8 + 6], v[c][h8 * 8 + 7]);
+            w.x = *reinterpret_cast<unsigned *>(&t0);
+            w.y = *reinterpret_cast<unsigned *>(&t1);
+            w.z = *reinterpret_cast<unsigned *>(&t2);
+            w.w = *reinterpret_cast<unsigned *>(&t3);
+            *reinterpret_cast<uint4 *>(prow + ((((c0 >> 3) + c * 2 + h8)) ^ (row & 7)) * 16) = w;
+          }
+        }
+      };
+      float sc[NB][16];
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < FT_BN; ++c) mx = fmaxf(mx, s[c]);
+      for (int c0 = 0; c0 < FT_BN; c0 += NB * 16) {
+        load_scores(c0, sc);
+#pragma unroll
+        for (int c = 0; c < NB; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, sc[c][i]);
+      }
       const float m_new = fmaxf(m_run, mx);
       const float moff = m_new == -INFINITY ? 0.f : m_new * scale_log2;
-      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run * scale_log2 - moff);
+      const float alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run * scale_log2 - moff);
       m_run = m_new;
-      float sum = 0.f;
-      // the row of P, 16 bytes (8 keys) at a time, where the tensor core expects it: row r lies at
-      // (r / 8) * 1024 + (r % 8) * 128, its 16-byte piece c at piece c ^ (r % 8)
-      unsigned char *prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+      // The buffer of P is free when the tensor core has finished the previous tile's product,
+      // which ran while this tile's maximum was being found.
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, status, 19));
+        if (!ok) break;
+      }
+      if (NB * 16 == FT_BN) {
+        write_p(0, sc, moff);
+      } else {
 #pragma unroll
-      for (int c8 = 0; c8 < FT_BN / 8; ++c8) {
-        float p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          p[i] = exp2f(fmaf(s[c8 * 8 + i], scale_log2, -moff));
-          sum += p[i];
+        for (int c0 = 0; c0 < FT_BN; c0 += NB * 16) {
+          load_scores(c0, sc);
+          write_p(c0, sc, moff);
         }
-        uint4 v;
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(p[0], p[1]), t1 = __floats2bfloat162_rn(p[2], p[3]),
-                       t2 = __floats2bfloat162_rn(p[4], p[5]), t3 = __floats2bfloat162_rn(p[6], p[7]);
-        v.x = *reinterpret_cast<unsigned *>(&t0);
-        v.y = *reinterpret_cast<unsigned *>(&t1);
-        v.z = *reinterpret_cast<unsigned *>(&t2);
-        v.w = *reinterpret_cast<unsigned *>(&t3);
-        *reinterpret_cast<uint4 *>(prow + ((c8 ^ (row & 7)) << 4)) = v;
       }
       l_run = l_run * alpha + sum;
+      tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core to read
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pfull);
-      // this tile's part of the output, when the tensor core has it
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, j & 1, abort_flag, status, 19));
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 16) {
-        float v[16];
-        tc_ld16(tmem_o + lane_addr + c0, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, v[i]);
+      // the previous tile's part of the output, while the tensor core works on this tile's
+      if (j > 0) {
+        tc_fence_after();
+        add_output(alpha_prev);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ofree);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ofree);
+      alpha_prev = alpha;
+    }
+    if (ok && n_tiles > 0) {                          // the last tile's part
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (n_tiles - 1) & 1, abort_flag, status, 20));
+      if (ok) {
+        tc_fence_after();
+        add_output(alpha_prev);
+        tc_fence_before();
+      }
     }
     if (ok && row < rows) {
       const float inv = 1.f / l_run;
@@ -291,7 +364,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 5) {
     tc_fence_after();
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
