@@ -3,15 +3,24 @@
 // tcgen05.mma, their accumulators in tensor memory and all operands brought by TMA.
 //
 // One CTA takes 128 query rows of one head of one sequence.  Its warps:
-//   warp 4    one lane loads the Q tile once and then, page by page, the K and V tiles (a page of
+//   warp 8    one lane loads the Q tile once and then, page by page, the K and V tiles (a page of
 //             the cache is a [64, d] block = one key tile) into a ring of shared-memory stages;
-//   warp 5    one lane issues S = Q K^T (operands K-major, 128-byte swizzle) into tensor memory and,
-//             when the probabilities are ready, O_j = P V_j (V is the MN-major operand: it lies
-//             [key][channel] in the cache and is used as it is) into a second accumulator;
-//   warps 0-3 a thread per query row: reads its row of S from tensor memory (no shuffles: the row is
-//             one lane), masks, keeps the running maximum and sum in 32-bit, writes the row of P as
-//             bfloat16 into shared memory in the swizzled layout the tensor core reads, then adds
-//             O_j to its output row scaled by exp(old maximum - new maximum).
+//   warp 9    one lane issues S = Q K^T (operands K-major, 128-byte swizzle) into one of two score
+//             buffers in tensor memory and, when the probabilities are ready, O += P V_j: P is the
+//             A operand straight from tensor memory, V the MN-major B operand (it lies
+//             [key][channel] in the cache and is used as it is); the output row stays in tensor
+//             memory from the first tile to the last;
+//   warps 0-7 two threads per query row (warp w and w + 4 reach the same 32 lanes of tensor memory),
+//             each with half of the tile's keys: reads its half of the row of S (no shuffles: a row
+//             is one lane), masks, exchanges the maximum with its partner through shared memory,
+//             exponentials and their sum in 32-bit, and writes its half of the row of P as packed
+//             bfloat16 over the scores it has just consumed.  Neither P nor O passes through
+//             shared memory, whose bandwidth the two products' other operands need.
+// The exponent's reference per row is not every tile's maximum: it moves only when a new maximum
+// exceeds it by more than 2^8 (in the exponent), and then, tile finished, the threads rescale the
+// output row in tensor memory and their sums.  P stays below 2^8, which bfloat16 and the 32-bit
+// accumulators hold as well as they hold [0, 1]; after the first tiles of a row the reference
+// seldom moves, so the output is seldom touched.
 // The score product of the next tile is issued as soon as the row threads have taken the current
 // scores out of tensor memory, so it runs under their exponentials; a second CTA on the same SM fills
 // the rest.  Exponentials are exp2 of scores pre-scaled by log2(e) / sqrt(d).
@@ -29,7 +38,7 @@ LLM_DEFINE_LAST_ERROR(llm_attention_prefill_tc_last_error)
 
 namespace {
 
-constexpr int FT_THREADS = 256;   // warps 0-3: a thread per query row; 4: loader; 5: tensor-core issue; 6, 7: none
+constexpr int FT_THREADS = 384;   // warps 0-7: two threads per query row; 8: loader; 9: tensor-core issue; 10, 11: none
 constexpr int FT_BM = 128;          // query rows per CTA
 constexpr int FT_BN = 64;           // keys per tile = tokens per page
 
@@ -38,13 +47,15 @@ struct FtShape {
   static constexpr int KB = D / 64;                         // 64-wide blocks of the head size
   static constexpr int Q_BYTES = FT_BM * D * 2;
   static constexpr int KV_BYTES = FT_BN * D * 2;            // one of K or V
-  static constexpr int P_BYTES = FT_BM * FT_BN * 2;
+  static constexpr int X_BYTES = 2 * 2 * FT_BM * 4;          // the partners' maxima, two tiles deep
   static constexpr int STAGES = D == 64 ? 4 : 2;
-  static constexpr int TMEM_COLS = 256;                     // two S buffers (64 columns each) + O_j (D columns)
-  static constexpr size_t SMEM = Q_BYTES + P_BYTES + (size_t)STAGES * 2 * KV_BYTES + 256;   // two CTAs per SM
-  // Registers move from the second warpgroup (loader, issuer) to the first (the row threads), which
-  // keep a row of the output and a row of scores each: 2 CTAs x 256 threads x 128 registers at launch.
-  static constexpr int REGS_FEW = 56, REGS_MANY = 256 - REGS_FEW;
+  static constexpr int TMEM_COLS = 256;                     // two S buffers (64 columns each) + O (D columns)
+  static constexpr size_t SMEM = Q_BYTES + X_BYTES + (size_t)STAGES * 2 * KV_BYTES + 256;   // two CTAs per SM
+  // Registers move from the third warpgroup (loader, issuer) to the row threads.  The CTA is launched
+  // with 80 registers a thread (2 CTAs x 384 threads on an SM), and what the row threads take must
+  // be what the third warpgroup gives up inside the same CTA: a request beyond that waits for ever.
+  static constexpr int REGS_LAUNCH = 80, REGS_FEW = 48, REGS_MANY = 96;
+  static_assert(128 * REGS_FEW + 256 * REGS_MANY <= FT_THREADS * REGS_LAUNCH, "register moves must balance within the CTA");
 };
 
 
@@ -54,7 +65,13 @@ __device__ __forceinline__ unsigned long long smem_desc_mn(unsigned addr) { retu
 
 __host__ __device__ constexpr unsigned instr_desc_mn(int m, int n) { return instr_desc(m, n) | (1u << 16); }
 
-// exp2 of a number that is never above zero here: one instruction (inputs of -inf give 0)
+// the largest of three in one instruction
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// exp2 of a number that is never far above zero here: one instruction (inputs of -inf give 0)
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -71,19 +88,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   using S = FtShape<D>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ __align__(1024) unsigned char smem[];
-  unsigned char *sQ = smem, *sP = smem + S::Q_BYTES, *sKV = sP + S::P_BYTES;
-  unsigned long long *bars = (unsigned long long *)(sKV + (size_t)STAGES * 2 * S::KV_BYTES);
-  // full[STAGES], empty[STAGES], q_full, s_full[2] (one per score buffer), p_full, o_full, o_free
+  unsigned char *sQ = smem, *sKV = smem + S::Q_BYTES;
+  float *xch = reinterpret_cast<float *>(sKV + (size_t)STAGES * 2 * S::KV_BYTES);       // [2][2][128]
+  unsigned long long *bars = (unsigned long long *)(xch + 4 * FT_BM);
+  // full[STAGES], empty[STAGES], q_full, s_full[2] (one per score buffer), p_full, o_full
   const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
   const unsigned bar_q = smem_u32(bars + 2 * STAGES), bar_sfull = bar_q + 8,
-                 bar_pfull = bar_q + 24, bar_ofull = bar_q + 32, bar_ofree = bar_q + 40;
+                 bar_pfull = bar_q + 24, bar_ofull = bar_q + 32;
   unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 6);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_dependents_launch();
   if (smem_u32(smem) & 1023u) {                               // swizzled tiles need 1024-byte alignment
-    if (threadIdx.x == 0) atomicCAS(status, 0, 21);
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, 21);
     return;
   }
   if (threadIdx.x == 0) {
@@ -94,13 +112,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(bar_q, 1);
     mbar_init(bar_sfull, 1);
     mbar_init(bar_sfull + 8, 1);
-    mbar_init(bar_pfull, 4);
+    mbar_init(bar_pfull, 8);
     mbar_init(bar_ofull, 1);
-    mbar_init(bar_ofree, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((unsigned)S::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -125,8 +142,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int n_tiles = last_tile - first_tile + 1;             // <= 0: nothing to do
   const int *pt = page_table + (size_t)b * pt_stride;
 
-  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
-  if (warp == 4) {
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
+  if (warp == 8) {
     // ------------------------------------------------------------ loader
     if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(bar_q, S::Q_BYTES);
@@ -159,11 +176,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ tensor-core issue
     if (lane == 0 && n_tiles > 0) {
       constexpr unsigned IDESC_S = instr_desc(FT_BM, FT_BN);          // S[128 x 64 keys], both operands K-major
-      constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, 64);          // O_j[128 x 64 channels], V MN-major
+      constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, 64);          // O[128 x 64 channels], V MN-major
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
       auto issue_s = [&](int j) {                                      // scores of tile j into buffer j & 1
         const int stage = j % STAGES;
@@ -191,8 +208,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tc_fence_after();
           issue_s(j + 1);
         }
-        ok = mbar_wait(bar_pfull, j & 1, abort_flag, status, 16) &&
-             mbar_wait(bar_ofree, (j & 1) ^ 1, abort_flag, status, 17);
+        ok = mbar_wait(bar_pfull, j & 1, abort_flag, status, 16);   // and the output row rescaled, if it had to be
         if (!ok) break;
         tc_fence_after();
         const int stage = j % STAGES;
@@ -201,170 +217,156 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int nb = 0; nb < S::KB; ++nb)           // 64 channels at a time
 #pragma unroll
           for (int kk = 0; kk < FT_BN / 16; ++kk)    // 16 keys: 32 bytes along P's rows, 16 rows of V
-            tc_mma(tmem_o + nb * 64, smem_desc(smem_u32(sP) + kk * 32),
-                   smem_desc_mn(va + nb * (FT_BN * 128) + kk * 2048), IDESC_O, kk > 0 ? 1u : 0u);
+            tc_mma_ts(tmem_o + nb * 64, tmem_s + (j & 1) * FT_BN + kk * 8,      // P lies over the scores' first columns
+                      smem_desc_mn(va + nb * (FT_BN * 128) + kk * 2048), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_ofull);
         tc_commit(bar_empty + 8 * stage);
       }
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------ a thread per query row
+  } else if (warp < 8) {
+    // ------------------------------------------------------------ two threads per query row
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(S::REGS_MANY));
-    const int quarter = warp;
+    const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
     const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
     const int pos = past + r0 + row;                           // the row's position in its sequence
-    float o[D];
-#pragma unroll
-    for (int c = 0; c < D; ++c) o[c] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
-    bool ok = true;
-    // o = o * a + (the tile's product in tensor memory), OB * 16 channels with OB loads in flight
-    constexpr int OB = D == 64 ? 4 : 2;
-    auto add_output = [&](float a) {
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += OB * 16) {
-        float t[OB][16];
-#pragma unroll
-        for (int c = 0; c < OB; ++c) tc_ld16_issue(tmem_o + lane_addr + c0 + c * 16, t[c]);
-        tc_ld_wait();
-#pragma unroll
-        for (int c = 0; c < OB; ++c) tc_ld_ready(t[c]);
-#pragma unroll
-        for (int c = 0; c < OB; ++c)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[c0 + c * 16 + i] = fmaf(o[c0 + c * 16 + i], a, t[c][i]);
-      }
-    };
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, status, 18));
-      if (!ok) break;
-      tc_fence_after();
+    constexpr int HD = D / 2;                                  // this thread's channels of the output row
+    const unsigned o_addr = tmem_o + lane_addr + half * HD;
+    float ref = -INFINITY;            // the exponent's reference, already times log2(e) / sqrt(d)
+    float l_run = 0.f;                // sum of this thread's exponentials, relative to ref
+    bool ok = n_tiles > 0;
+    // Partners meet at a hardware barrier in every tile, so neither leaves the loop early: a thread
+    // whose wait ran out goes on through the barriers without working.
+    for (int j = 0; j < n_tiles; ++j) {
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, status, 18));
       const unsigned s_addr = tmem_s + (j & 1) * FT_BN + lane_addr;
-      const int k0 = (first_tile + j) * FT_BN;
-      const bool edge = (k0 + FT_BN - 1 > past + r0) || (window > 0 && k0 <= past + r0 + FT_BM - 1 - window);
-      // The row's scores come into registers NB * 16 at a time, with NB loads in flight and one wait.
-      // A head size of 64 leaves room for the whole row (NB = 4), which is then read once; a larger
-      // one reads it twice, first for the maximum and then for the exponentials.
-      constexpr int NB = D == 64 ? 4 : 2;
-      auto load_scores = [&](int c0, float (&v)[NB][16]) {
-#pragma unroll
-        for (int c = 0; c < NB; ++c) tc_ld16_issue(s_addr + c0 + c * 16, v[c]);
-        tc_ld_wait();
-#pragma unroll
-        for (int c = 0; c < NB; ++c) tc_ld_ready(v[c]);
-        if (edge) {
-#pragma unroll
-          for (int c = 0; c < NB; ++c)
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int key = k0 + c0 + c * 16 + i;
-              if (!(key <= pos && (window <= 0 || key > pos - window))) v[c][i] = -INFINITY;
-            }
-        }
-      };
-      // exponentials of NB * 16 scores and their pieces of the row of P, 16 bytes (8 keys) at a time,
-      // where the tensor core expects it: row r lies at (r / 8) * 1024 + (r % 8) * 128, its 16-byte
-      // piece c at piece c ^ (r % 8)
-      unsigned char *prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
-      float sum = 0.f;
-      auto write_p = [&](int c0, float (&v)[NB][16], float moff) {
-#pragma unroll
-        for (int c = 0; c < NB; ++c) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            v[c][i] = fast_exp2(fmaf(v[c][i], scale_log2, -moff));
-            sum += v[c][i];
-          }
-#pragma unroll
-          for (int h8 = 0; h8 < 2; ++h8) {
-            uint4 w;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[c][h8 * 8], v[c][h8 * 8 + 1]),
-                           t1 = __floats2bfloat162_rn(v[c][h8 * 8 + 2], v[c][h8 * 8 + 3]),
-                           t2 = __floats2bfloat162_rn(v[c][h8 * 8 + 4], v[c][h8 * 8 + 5]),
-                           t3 = __floats2bfloat162_rn(v[c][h8 * 8 + 6], v[c][h8 * 8 + 7]);
-            w.x = *reinterpret_cast<unsigned *>(&t0);
-            w.y = *reinterpret_cast<unsigned *>(&t1);
-            w.z = *reinterpret_cast<unsigned *>(&t2);
-            w.w = *reinterpret_cast<unsigned *>(&t3);
-            *reinterpret_cast<uint4 *>(prow + ((((c0 >> 3) + c * 2 + h8)) ^ (row & 7)) * 16) = w;
-          }
-        }
-      };
-      float sc[NB][16];
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c0 = 0; c0 < FT_BN; c0 += NB * 16) {
-        load_scores(c0, sc);
-#pragma unroll
-        for (int c = 0; c < NB; ++c)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, sc[c][i]);
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float moff = m_new == -INFINITY ? 0.f : m_new * scale_log2;
-      const float alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run * scale_log2 - moff);
-      m_run = m_new;
-      // The buffer of P is free when the tensor core has finished the previous tile's product,
-      // which ran while this tile's maximum was being found.
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, status, 19));
-        if (!ok) break;
-      }
-      if (NB * 16 == FT_BN) {
-        write_p(0, sc, moff);
-      } else {
-#pragma unroll
-        for (int c0 = 0; c0 < FT_BN; c0 += NB * 16) {
-          load_scores(c0, sc);
-          write_p(c0, sc, moff);
-        }
-      }
-      l_run = l_run * alpha + sum;
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core to read
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull);
-      // the previous tile's part of the output, while the tensor core works on this tile's
-      if (j > 0) {
-        tc_fence_after();
-        add_output(alpha_prev);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ofree);
-      }
-      alpha_prev = alpha;
-    }
-    if (ok && n_tiles > 0) {                          // the last tile's part
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (n_tiles - 1) & 1, abort_flag, status, 20));
+      const int k0 = (first_tile + j) * FT_BN + half * 32;    // this thread's first key
+      float own[2][16];
+      float *xrow = xch + (j & 1) * 2 * FT_BM + row;
       if (ok) {
         tc_fence_after();
-        add_output(alpha_prev);
+        tc_ld16_issue(s_addr + half * 32, own[0]);
+        tc_ld16_issue(s_addr + half * 32 + 16, own[1]);
+        tc_ld_wait();
+        tc_ld_ready(own[0]);
+        tc_ld_ready(own[1]);
+        if ((k0 + 31 > past + r0) || (window > 0 && k0 <= past + r0 + FT_BM - 1 - window)) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int key = k0 + c * 16 + i;
+              if (!(key <= pos && (window <= 0 || key > pos - window))) own[c][i] = -INFINITY;
+            }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) mx = max3(mx, own[c][i], own[c][i + 1]);
+        xrow[half * FT_BM] = mx;
         tc_fence_before();
       }
-    }
-    if (ok && row < rows) {
-      const float inv = 1.f / l_run;
-      __nv_bfloat16 *dst = out + (size_t)(q0 + r0 + row) * out_stride + (size_t)h * D;
+      // Past this barrier the partner has its maximum in shared memory and its scores in registers,
+      // so the probabilities may be written over them.
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      if (!ok) continue;
+      const float mxs = fmaxf(xrow[0], xrow[FT_BM]) * scale_log2;
+      if (__any_sync(0xffffffffu, mxs > ref + 8.f)) {          // a warp decides as one: the loads below are its own
+        const float new_ref = fmaxf(ref, mxs);
+        const float alpha = new_ref == -INFINITY ? 1.f : fast_exp2(ref - new_ref);
+        if (j > 0) {
+          // the output row may be touched when the tensor core has finished the previous tile's product
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, status, 19));
+          if (!ok) continue;
+          tc_fence_after();
 #pragma unroll
-      for (int c8 = 0; c8 < D / 8; ++c8) {
-        uint4 v;
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv),
-                       t1 = __floats2bfloat162_rn(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv),
-                       t2 = __floats2bfloat162_rn(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv),
-                       t3 = __floats2bfloat162_rn(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
-        v.x = *reinterpret_cast<unsigned *>(&t0);
-        v.y = *reinterpret_cast<unsigned *>(&t1);
-        v.z = *reinterpret_cast<unsigned *>(&t2);
-        v.w = *reinterpret_cast<unsigned *>(&t3);
-        *reinterpret_cast<uint4 *>(dst + c8 * 8) = v;
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            float t[2][16];
+            tc_ld16_issue(o_addr + c0, t[0]);
+            tc_ld16_issue(o_addr + c0 + 16, t[1]);
+            tc_ld_wait();
+            tc_ld_ready(t[0]);
+            tc_ld_ready(t[1]);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) t[c][i] *= alpha;
+              tc_st16(o_addr + c0 + c * 16, t[c]);
+            }
+          }
+        }
+        l_run *= alpha;
+        ref = new_ref;
       }
+      const float moff = ref == -INFINITY ? 0.f : ref;
+      // two scores to an instruction for the scaling and for the sum (packed 32-bit pairs)
+      float2 sum2 = make_float2(0.f, 0.f);
+      const float2 scale2 = make_float2(scale_log2, scale_log2), off2 = make_float2(-moff, -moff);
+      unsigned pk[16];                                        // the half row of P: two keys to a column
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float (&v)[16] = own[c];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), scale2, off2);
+          const float e0 = fast_exp2(t.x), e1 = fast_exp2(t.y);
+          sum2 = __fadd2_rn(sum2, make_float2(e0, e1));
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+          pk[c * 8 + (i >> 1)] = *reinterpret_cast<const unsigned *>(&b2);
+        }
+      }
+      l_run += sum2.x + sum2.y;
+      tc_st16(s_addr + half * 16, pk);
+      tc_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pfull);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (n_tiles - 1) & 1, abort_flag, status, 20));
+    // The row's sum is the two threads' sums, first half first.  Every row warp comes here, whatever
+    // happened above.
+    asm volatile("bar.sync 5, 256;" ::: "memory");          // the last tile's maxima have been read
+    xch[half * FT_BM + row] = l_run;
+    asm volatile("bar.sync 5, 256;" ::: "memory");
+    const float l_row = xch[row] + xch[FT_BM + row];
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.f / l_row;
+      __nv_bfloat16 *dst = out + (size_t)(q0 + r0 + row) * out_stride + (size_t)h * D + half * HD;
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float t[2][16];
+        tc_ld16_issue(o_addr + c0, t[0]);
+        tc_ld16_issue(o_addr + c0 + 16, t[1]);
+        tc_ld_wait();
+        tc_ld_ready(t[0]);
+        tc_ld_ready(t[1]);
+        if (row < rows) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int h8 = 0; h8 < 2; ++h8) {
+              uint4 v;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(t[c][h8 * 8] * inv, t[c][h8 * 8 + 1] * inv),
+                             t1 = __floats2bfloat162_rn(t[c][h8 * 8 + 2] * inv, t[c][h8 * 8 + 3] * inv),
+                             t2 = __floats2bfloat162_rn(t[c][h8 * 8 + 4] * inv, t[c][h8 * 8 + 5] * inv),
+                             t3 = __floats2bfloat162_rn(t[c][h8 * 8 + 6] * inv, t[c][h8 * 8 + 7] * inv);
+              v.x = *reinterpret_cast<unsigned *>(&t0);
+              v.y = *reinterpret_cast<unsigned *>(&t1);
+              v.z = *reinterpret_cast<unsigned *>(&t2);
+              v.w = *reinterpret_cast<unsigned *>(&t3);
+              *reinterpret_cast<uint4 *>(dst + c0 + c * 16 + h8 * 8) = v;
+            }
+        }
+      }
+      tc_fence_before();
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
