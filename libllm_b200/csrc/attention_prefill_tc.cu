@@ -6,10 +6,11 @@
 //   warp 8    one lane loads the Q tile once and then, page by page, the K and V tiles (a page of
 //             the cache is a [64, d] block = one key tile) into a ring of shared-memory stages;
 //   warp 9    one lane issues S = Q K^T (operands K-major, 128-byte swizzle) into one of two score
-//             buffers in tensor memory and, when the probabilities are ready, O += P V_j: P is the
-//             A operand straight from tensor memory, V the MN-major B operand (it lies
-//             [key][channel] in the cache and is used as it is); the output row stays in tensor
-//             memory from the first tile to the last;
+//             buffers in tensor memory;
+//   warp 10   one lane issues, when the probabilities are ready, O += P V_j: P is the A operand
+//             straight from tensor memory, V the MN-major B operand (it lies [key][channel] in the
+//             cache and is used as it is); the output row stays in tensor memory from the first
+//             tile to the last;
 //   warps 0-7 two threads per query row (warp w and w + 4 reach the same 32 lanes of tensor memory),
 //             each with half of the tile's keys: reads its half of the row of S (no shuffles: a row
 //             is one lane), masks, exchanges the maximum with its partner through shared memory,
@@ -21,9 +22,10 @@
 // output row in tensor memory and their sums.  P stays below 2^8, which bfloat16 and the 32-bit
 // accumulators hold as well as they hold [0, 1]; after the first tiles of a row the reference
 // seldom moves, so the output is seldom touched.
-// The score product of the next tile is issued as soon as the row threads have taken the current
-// scores out of tensor memory, so it runs under their exponentials; a second CTA on the same SM fills
-// the rest.  Exponentials are exp2 of scores pre-scaled by log2(e) / sqrt(d).
+// With two score buffers the scores of tile j + 1 are computed while the row threads work on tile j;
+// a buffer is written again when the output product has read the probabilities that lay over it.  A
+// second CTA on the same SM fills the rest.  Exponentials are exp2 of scores pre-scaled by
+// log2(e) / sqrt(d).
 //
 // Semantics as the other attention kernels: token i of a sequence that stands behind `past` cached
 // ones sees keys 0..past+i (src/flint/operators.cc:119-124), head h reads kv head h / (heads /
@@ -38,7 +40,7 @@ LLM_DEFINE_LAST_ERROR(llm_attention_prefill_tc_last_error)
 
 namespace {
 
-constexpr int FT_THREADS = 384;   // warps 0-7: two threads per query row; 8: loader; 9: tensor-core issue; 10, 11: none
+constexpr int FT_THREADS = 384;   // warps 0-7: two threads per query row; 8: loader; 9, 10: tensor-core issue; 11: none
 constexpr int FT_BM = 128;          // query rows per CTA
 constexpr int FT_BN = 64;           // keys per tile = tokens per page
 
@@ -91,11 +93,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char *sQ = smem, *sKV = smem + S::Q_BYTES;
   float *xch = reinterpret_cast<float *>(sKV + (size_t)STAGES * 2 * S::KV_BYTES);       // [2][2][128]
   unsigned long long *bars = (unsigned long long *)(xch + 4 * FT_BM);
-  // full[STAGES], empty[STAGES], q_full, s_full[2] (one per score buffer), p_full, o_full
+  // full[STAGES], empty[STAGES], q_full, s_full[2] (one per score buffer), p_full, o_full, pv_done[2]
   const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
   const unsigned bar_q = smem_u32(bars + 2 * STAGES), bar_sfull = bar_q + 8,
-                 bar_pfull = bar_q + 24, bar_ofull = bar_q + 32;
-  unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 6);
+                 bar_pfull = bar_q + 24, bar_ofull = bar_q + 32, bar_pvdone = bar_q + 40;
+  unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 7);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -114,6 +116,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(bar_sfull + 8, 1);
     mbar_init(bar_pfull, 8);
     mbar_init(bar_ofull, 1);
+    mbar_init(bar_pvdone, 1);
+    mbar_init(bar_pvdone + 8, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -177,13 +181,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------ tensor-core issue
+    // ------------------------------------------------------------ tensor-core issue: scores
+    // The two products have an issuing thread each: what a thread spends on an instruction
+    // (descriptors, the hand-over to the tensor core) is more than the instruction takes to run.
     if (lane == 0 && n_tiles > 0) {
       constexpr unsigned IDESC_S = instr_desc(FT_BM, FT_BN);          // S[128 x 64 keys], both operands K-major
-      constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, 64);          // O[128 x 64 channels], V MN-major
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
-      auto issue_s = [&](int j) {                                      // scores of tile j into buffer j & 1
+      for (int j = 0; j < n_tiles && ok; ++j) {
         const int stage = j % STAGES;
+        ok = mbar_wait(bar_full + 8 * stage, (j / STAGES) & 1, abort_flag, status, 13);
+        // buffer j & 1 last held the scores of tile j - 2 and then its probabilities, which the
+        // other thread's product has to have read
+        if (ok && j >= 2) ok = mbar_wait(bar_pvdone + 8 * (j & 1), ((j >> 1) - 1) & 1, abort_flag, status, 14);
+        if (!ok) break;
+        tc_fence_after();
         const unsigned ka = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < S::KB; ++kb)
@@ -192,34 +203,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tc_mma(tmem_s + (j & 1) * FT_BN, smem_desc(smem_u32(sQ) + kb * (FT_BM * 128) + kk * 32),
                    smem_desc(ka + kb * (FT_BN * 128) + kk * 32), IDESC_S, (kb > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_sfull + 8 * (j & 1));
-      };
-      if (ok) ok = mbar_wait(bar_full, 0, abort_flag, status, 13);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
       }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ tensor-core issue: output
+    if (lane == 0 && n_tiles > 0) {
+      constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, 64);          // O[128 x 64 channels], V MN-major
+      bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          // The next tile's scores go into the other buffer at once: its last reader was tile
-          // j - 1, whose probabilities this thread has already waited for.
-          const int s1 = (j + 1) % STAGES;
-          ok = mbar_wait(bar_full + 8 * s1, ((j + 1) / STAGES) & 1, abort_flag, status, 14);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(j + 1);
-        }
-        ok = mbar_wait(bar_pfull, j & 1, abort_flag, status, 16);   // and the output row rescaled, if it had to be
+        const int stage = j % STAGES;
+        ok = mbar_wait(bar_full + 8 * stage, (j / STAGES) & 1, abort_flag, status, 15) &&
+             mbar_wait(bar_pfull, j & 1, abort_flag, status, 16);   // and the output row rescaled, if it had to be
         if (!ok) break;
         tc_fence_after();
-        const int stage = j % STAGES;
         const unsigned va = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES) + S::KV_BYTES;
 #pragma unroll
         for (int nb = 0; nb < S::KB; ++nb)           // 64 channels at a time
 #pragma unroll
-          for (int kk = 0; kk < FT_BN / 16; ++kk)    // 16 keys: 32 bytes along P's rows, 16 rows of V
+          for (int kk = 0; kk < FT_BN / 16; ++kk)    // 16 keys: 8 columns of P, 16 rows of V
             tc_mma_ts(tmem_o + nb * 64, tmem_s + (j & 1) * FT_BN + kk * 8,      // P lies over the scores' first columns
                       smem_desc_mn(va + nb * (FT_BN * 128) + kk * 2048), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_ofull);
+        tc_commit(bar_pvdone + 8 * (j & 1));
         tc_commit(bar_empty + 8 * stage);
       }
     }
