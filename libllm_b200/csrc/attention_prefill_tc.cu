@@ -264,12 +264,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
               if (!(key <= pos && (window <= 0 || key > pos - window))) own[c][i] = -INFINITY;
             }
         }
-        float mx = -INFINITY;
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of sixteen
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) mx = max3(mx, own[c][i], own[c][i + 1]);
-        xrow[half * FT_BM] = mx;
+          for (int i = 0; i < 16; i += 2) m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], own[c][i], own[c][i + 1]);
+        xrow[half * FT_BM] = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
         tc_fence_before();
       }
       // Past this barrier the partner has its maximum in shared memory and its scores in registers,
@@ -306,7 +306,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       const float moff = ref == -INFINITY ? 0.f : ref;
       // two scores to an instruction for the scaling and for the sum (packed 32-bit pairs)
-      float2 sum2 = make_float2(0.f, 0.f);
+      float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       const float2 scale2 = make_float2(scale_log2, scale_log2), off2 = make_float2(-moff, -moff);
       unsigned pk[16];                                        // the half row of P: two keys to a column
 #pragma unroll
@@ -316,11 +316,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int i = 0; i < 16; i += 2) {
           const float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), scale2, off2);
           const float e0 = fast_exp2(t.x), e1 = fast_exp2(t.y);
-          sum2 = __fadd2_rn(sum2, make_float2(e0, e1));
+          sum4[(i >> 1) & 3] = __fadd2_rn(sum4[(i >> 1) & 3], make_float2(e0, e1));
           const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
           pk[c * 8 + (i >> 1)] = *reinterpret_cast<const unsigned *>(&b2);
         }
       }
+      const float2 sum2 = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
       l_run += sum2.x + sum2.y;
       tc_st16(s_addr + half * 16, pk);
       tc_st_wait();

@@ -559,3 +559,30 @@ def test_attention_prefill_on_tcgen05_finds_a_far_key_and_respects_the_window_ed
         close(out.view(L, 1, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
         near = float((out[700].float().cpu() - vs[0][3, 0].float()).abs().max()) < 0.2
         assert near == sees, (window, near)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("step_nats", [6.5, 2.0, -6.5])
+def test_attention_prefill_on_tcgen05_when_the_maximum_moves_from_tile_to_tile(d, step_nats):
+    """The kernel moves a row's exponent reference only when a tile's maximum exceeds it by 2^8, and
+    then rescales the output row in tensor memory.  Random scores settle the reference in the first
+    tile; here every 64 keys the scores step up by 6.5 nats (the reference moves in every tile and
+    earlier tiles all but vanish), by 2 nats (it lags behind the maximum, moving every third tile or
+    so, and the probabilities in between exceed 1), or down (it never moves after the first tile)."""
+    from libllm_b200.csrc import ops
+    page, L, n_heads, n_kv = 64, 700, 2, 1
+    K, V, table, ks, vs = paged_cache(1, [L], n_kv, d, page, "bfloat16", 75)
+    q = rnd((L, n_heads * d), "bfloat16", 76, 0.3)
+    q.view(L, n_heads, d)[:, :, 0] = math.sqrt(d)              # channel 0 alone gives key j's score k[j, 0]
+    k = ks[0][:, 0].float() * 0.3
+    k[:, 0] = step_nats * (torch.arange(L) // 64).float()
+    ks[0][:, 0] = k.to(torch.bfloat16)
+    for lp in range((L + page - 1) // page):
+        n = min(page, L - lp * page)
+        K[int(table[0, lp]), 0, :n] = ks[0][lp * page:lp * page + n, 0].to(DEV)
+    start, past = prefill_inputs([L], [L])
+    out = torch.full((L, n_heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, n_heads, n_kv, d, page, None, 1 / math.sqrt(d))
+    ops.check_tc_status()
+    ref = P.attention_scores_softmax_values(q.cpu().view(L, n_heads, d), ks[0], vs[0], None)
+    close(out.view(L, n_heads, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
