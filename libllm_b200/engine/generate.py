@@ -8,10 +8,9 @@ and then one token per live sequence per step, drops sequences as they end (thei
 slots and pages go back at once) and starts the next batch when a batch is done."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Callable, Iterable, Iterator, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Callable, Iterable, List, Optional, Sequence, Tuple
 
-import torch
 
 from ..errors import CacheError, InvalidArgError
 from ..sampling.rng import uniform

@@ -4,7 +4,6 @@ architectures; the architecture's name is used once, to look up the function tha
 describes it (libllm_b200/config/base.py)."""
 from __future__ import annotations
 
-import os
 from typing import Dict, List, Optional
 
 import torch

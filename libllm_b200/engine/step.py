@@ -14,7 +14,7 @@ copied into the graph's fixed buffer before each replay."""
 from __future__ import annotations
 
 import gc
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -22,7 +22,7 @@ import torch
 
 from ..cache import KVCache
 from ..csrc import ops
-from ..errors import CacheError, InvalidArgError
+from ..errors import InvalidArgError
 from ..parts.base import StepContext
 from .model import Model
 

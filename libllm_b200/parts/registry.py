@@ -5,7 +5,7 @@ registers itself with ``register_part`` and is then chosen by any spec that carr
 kind; no file of the library has to change for that."""
 from __future__ import annotations
 
-from typing import Dict, Tuple, Type
+from typing import Dict, Tuple
 
 from ..errors import ConfigError
 

@@ -9,7 +9,7 @@ it is used in.  The reference builds its one architecture in code
 those build functions."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Optional, Tuple
 
 

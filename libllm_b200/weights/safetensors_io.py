@@ -12,7 +12,7 @@ import mmap
 import os
 import struct
 import warnings
-from typing import Dict, Iterable, List, Mapping, Tuple
+from typing import Dict, List, Mapping, Tuple
 
 import numpy as np
 import torch

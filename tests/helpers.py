@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import os
 import tempfile
-from typing import Dict, List, Sequence
+from typing import Dict, List
 
 import torch
 

@@ -3,10 +3,9 @@ cutting the work: whole requests, the last 32 tokens one by one, batches of uneq
 lengths whose shorter requests end earlier with slots used again, long decoding, and the
 first tokens of a sequence."""
 import pytest
-import torch
 
 import plain_llama as P
-from helpers import TINY, check_against_plain, check_logits, model_folder, plain_weights, tokens_for
+from helpers import check_against_plain, model_folder, plain_weights, tokens_for
 from replay import replay_batch
 
 pytestmark = pytest.mark.gpu

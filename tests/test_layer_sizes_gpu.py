@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_llama as P
-from helpers import TOL, check_logits, model_folder, plain_weights, rel_err, rms_err
+from helpers import TOL, model_folder, plain_weights, rel_err, rms_err
 from replay import replay_batch
 
 pytestmark = pytest.mark.gpu

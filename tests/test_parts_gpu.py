@@ -1,6 +1,5 @@
 """Each part a layer is put together from, built from its spec and run alone against the
 plain implementation's function for it, at sizes other than the tiny models'."""
-import math
 
 import pytest
 import torch

@@ -11,9 +11,7 @@ stepped through the library's engine without a change to the library's files:
 The toy parts compute with torch operators on the device (they are test doubles, not
 product kernels); the plain implementation below restates the same model on the CPU in
 float64 for whole sequences.  None of this is a model of the reference's or of anyone's."""
-import math
 from dataclasses import dataclass
-from typing import Dict, List, Optional
 
 import pytest
 import torch
