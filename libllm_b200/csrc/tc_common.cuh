@@ -35,6 +35,15 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// The same, but the thread may sleep in the hardware for up to `ns` until the phase completes: a
+// waiting warp then takes no issue slots from the working ones.
+__device__ __forceinline__ bool mbar_try_sleep(unsigned bar, unsigned parity, unsigned ns) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
 // Waits for the barrier's phase with a time limit.  Returns false when the limit ran out or
 // another warp has given up (`*abort_flag` set); the first to give up records `code`.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, int *status,
@@ -42,8 +51,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = globaltimer();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try(bar, parity)) return true;
+    for (int i = 0; i < 8; ++i)
+      if (mbar_try_sleep(bar, parity, 20000u)) return true;
     if (*abort_flag) return mbar_try(bar, parity);
     if (globaltimer() - t0 > TC_WAIT_NS) {
       *abort_flag = 1;

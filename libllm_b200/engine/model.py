@@ -11,6 +11,7 @@ import torch
 from ..config import ModelConfig, architecture_for, load_config
 from ..csrc import build, ops
 from ..errors import ConfigError, InvalidArgError
+from ..parts import fast
 from ..parts.base import BuildEnv, CacheNeed, ResidualStream, StateNeed, StepContext
 from ..parts.linear import linear
 from ..parts.registry import build_part
@@ -85,7 +86,7 @@ class Model:
         return self
 
     def kernel_families(self) -> List[str]:
-        fams = {"elementwise", "gemm_plain", "sampling", "gemv", "gemm_tc"}
+        fams = {"elementwise", "sampling", *fast.product_families(self.dtype)}
         for layer in self.layers:
             fams.update(layer.kernel_families())
         return sorted(fams)

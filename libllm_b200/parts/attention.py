@@ -56,7 +56,7 @@ class Attention(Mixer):
             self.b_qkv = torch.cat([fetch(n).to(torch.float32) for n in needs[4:7]]).contiguous()
 
     def kernel_families(self) -> List[str]:
-        return ["rope", "attention_generic", "gemm_plain", "gemv", "gemm_tc", "attention_decode", "attention_decode_tc", "attention_prefill", "attention_prefill_tc"]
+        return fast.product_families(self.env.dtype) + fast.attention_families(self.spec, self.env.dtype, self.env.page_size)
 
     def cache_need(self) -> Optional[CacheNeed]:
         s = self.spec

@@ -4,7 +4,7 @@ switched off by an environment variable to compare it with the general one."""
 from __future__ import annotations
 
 import os
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -29,6 +29,37 @@ SM_COUNT = 148
 # streamer reads its tokens through L1 and slows down when a kernel with much shared memory runs
 # beside it, and above 16 tokens it falls behind (661 us against 181 us for a layer's products at 64).
 GEMV_TOKENS = int(os.environ.get("LIBLLM_B200_GEMV_TOKENS", "0"))
+
+
+def product_families(dtype: torch.dtype) -> List[str]:
+    """Kernel families that the products of an engine of this type launch (compiled when the model
+    is built; a family that a rare case needs beyond these is compiled when that case comes)."""
+    fams = ["gemm_plain"]                      # the 32-bit path; with bfloat16, products with a bias
+    if dtype == torch.bfloat16:
+        if ENABLED["gemm_tc"] and PRODUCT == "tc":
+            fams.append("gemm_tc")
+        if ENABLED["gemv"] and (GEMV_TOKENS > 0 or PRODUCT != "tc"):
+            fams.append("gemv")
+    return fams
+
+
+def attention_families(spec, dtype: torch.dtype, page_size: int) -> List[str]:
+    """The same for an attention part with this head size, grouping and page size."""
+    fams = ["rope", "attention_generic"]
+    if dtype != torch.bfloat16:
+        return fams
+    d, group = spec.head_dim, spec.n_heads // spec.n_kv_heads
+    tiled = page_size == 64 and d % 16 == 0 and 16 <= d <= 128
+    if ENABLED["prefill_attention_tc"] and page_size == 64 and d in (64, 128):
+        fams.append("attention_prefill_tc")
+    elif ENABLED["prefill_attention"] and tiled:
+        fams.append("attention_prefill")
+    fused = ENABLED["decode_attention_tc"] and tiled and group <= 16 and not spec.bias and spec.position is not None
+    if fused:
+        fams.append("attention_decode_tc")
+    elif ENABLED["decode_attention"] and d in (16, 32, 64, 128) and group in (1, 2, 3, 4, 8):
+        fams.append("attention_decode")
+    return fams
 
 
 def small_batch_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,

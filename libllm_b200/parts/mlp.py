@@ -30,7 +30,7 @@ class SwiGLU(FeedForward):
         self.w_down = fetch(needs[2])
 
     def kernel_families(self) -> List[str]:
-        return ["elementwise", "gemm_plain", "gemv", "gemm_tc"]
+        return ["elementwise"] + fast.product_families(self.env.dtype)
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
         m = None
