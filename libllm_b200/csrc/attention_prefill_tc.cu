@@ -61,10 +61,9 @@ struct FtShape {
 };
 
 
-// MN-major operand descriptor: the tile lies [k][64 channels] in 128-byte swizzled rows, 8 rows of k
-// per 1024 bytes (checked on the device: 16 k further = 2048 bytes further).
-__device__ __forceinline__ unsigned long long smem_desc_mn(unsigned addr) { return smem_desc(addr); }
-
+// V as the MN-major operand: a tile lies [key][64 channels] in 128-byte swizzled rows, 8 keys per
+// 1024 bytes (checked on the device: 16 keys further = 2048 bytes further); a second block of 64
+// channels lies a whole tile (64 keys x 128 bytes) further on, which the descriptor's leading offset says.
 __host__ __device__ constexpr unsigned instr_desc_mn(int m, int n) { return instr_desc(m, n) | (1u << 16); }
 
 // the largest of three in one instruction
@@ -208,7 +207,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   } else if (warp == 10) {
     // ------------------------------------------------------------ tensor-core issue: output
     if (lane == 0 && n_tiles > 0) {
-      constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, 64);          // O[128 x 64 channels], V MN-major
+      constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, D);           // O[128 x D channels], V MN-major
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int stage = j % STAGES;
@@ -217,12 +216,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!ok) break;
         tc_fence_after();
         const unsigned va = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES) + S::KV_BYTES;
+        // 16 keys to a product: 8 columns of P (it lies over the scores' first columns), 16 rows of
+        // V; all D channels at once, the second block of 64 channels FT_BN rows further on
 #pragma unroll
-        for (int nb = 0; nb < S::KB; ++nb)           // 64 channels at a time
-#pragma unroll
-          for (int kk = 0; kk < FT_BN / 16; ++kk)    // 16 keys: 8 columns of P, 16 rows of V
-            tc_mma_ts(tmem_o + nb * 64, tmem_s + (j & 1) * FT_BN + kk * 8,      // P lies over the scores' first columns
-                      smem_desc_mn(va + nb * (FT_BN * 128) + kk * 2048), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < FT_BN / 16; ++kk)
+          tc_mma_ts(tmem_o, tmem_s + (j & 1) * FT_BN + kk * 8, smem_desc_lbo(va + kk * 2048, FT_BN * 128), IDESC_O,
+                    (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_ofull);
         tc_commit(bar_pvdone + 8 * (j & 1));
         tc_commit(bar_empty + 8 * stage);

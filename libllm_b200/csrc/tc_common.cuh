@@ -142,6 +142,17 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
   d |= 2ull << 61;
   return d;
 }
+// The same with a leading offset: for an MN-major operand wider than one 128-byte row of 64
+// elements, the distance in bytes from one block of 64 along MN to the next.
+__device__ __forceinline__ unsigned long long smem_desc_lbo(unsigned addr, unsigned lbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
 // Instruction descriptor of kind::f16: D in 32-bit floats (bits 4-5 = 1), A and B bfloat16 (bits 7-9
 // and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
 __host__ __device__ constexpr unsigned instr_desc(int m, int n) {
