@@ -380,19 +380,52 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int idx = tid; idx < G * D; idx += DT_WARPS * 32) {
-    const int h = idx / D, c = idx % D;
-    const int head = kvh * G + h;
-    const size_t slot0 = ((size_t)b * n_heads + head) * n_splits;
-    float M = -INFINITY;
-    for (int s = n_active_first; s <= n_active_last; ++s) M = fmaxf(M, __ldcg(ws_ml + (slot0 + s) * 2));
-    float L = 0.f, O = 0.f;
-    for (int s = n_active_first; s <= n_active_last; ++s) {
-      const float f = exp2f(__ldcg(ws_ml + (slot0 + s) * 2) - M);
-      L += __ldcg(ws_ml + (slot0 + s) * 2 + 1) * f;
-      O += __ldcg(ws_o + (slot0 + s) * D + c) * f;
+  // The splits' results come from L2, which answers slowly while the next product's CTAs fill their
+  // rings: every thread issues all loads of a batch of splits for its two channels before it uses
+  // any, and the (maximum, sum) pairs of the batch, which all channels of a head share, come into
+  // shared memory once.  A thread waits for memory once a batch; the sums keep the split order.
+  constexpr int JB = 16;
+  float2 *s_ml = reinterpret_cast<float2 *>(sK) + (size_t)DT_WARPS * DT_ROWS * D / 2;   // [G][JB], behind sm_o
+  for (int base = 0; base < G * D / 2; base += DT_WARPS * 32) {      // a channel pair per thread (one round for a group of 4 heads of 64)
+    const int idx = base + tid;
+    const bool mine = idx < G * D / 2;
+    const int h = mine ? idx / (D / 2) : 0, c = mine ? (idx % (D / 2)) * 2 : 0;
+    const size_t my_slot0 = ((size_t)b * n_heads + kvh * G + h) * n_splits;
+    float M = -INFINITY, L = 0.f, O0 = 0.f, O1 = 0.f;
+    for (int s0 = n_active_first; s0 <= n_active_last; s0 += JB) {
+      float2 ov[JB];
+#pragma unroll
+      for (int j = 0; j < JB; ++j)
+        ov[j] = __ldcg(reinterpret_cast<const float2 *>(ws_o + (my_slot0 + min(s0 + j, n_active_last)) * D + c));
+      for (int i = tid; i < G * JB; i += DT_WARPS * 32) {
+        const int hh = i / JB, j = i % JB;
+        const size_t slot0 = ((size_t)b * n_heads + kvh * G + hh) * n_splits;
+        float2 ml = __ldcg(reinterpret_cast<const float2 *>(ws_ml + (slot0 + min(s0 + j, n_active_last)) * 2));
+        if (s0 + j > n_active_last) ml = make_float2(-INFINITY, 0.f);
+        s_ml[i] = ml;
+      }
+      __syncthreads();
+      float Mb = M;
+#pragma unroll
+      for (int j = 0; j < JB; ++j) Mb = fmaxf(Mb, s_ml[h * JB + j].x);
+      const float keep = M == -INFINITY ? 0.f : exp2f(M - Mb);      // what was summed so far, to the new maximum
+      L *= keep;
+      O0 *= keep;
+      O1 *= keep;
+      M = Mb;
+#pragma unroll
+      for (int j = 0; j < JB; ++j) {
+        const float2 ml = s_ml[h * JB + j];
+        const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - Mb);
+        L += ml.y * f;
+        O0 += ov[j].x * f;
+        O1 += ov[j].y * f;
+      }
+      __syncthreads();
     }
-    out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L);
+    if (mine)
+      *reinterpret_cast<__nv_bfloat162 *>(out + (size_t)b * out_stride + (size_t)(kvh * G + h) * D + c) =
+          __floats2bfloat162_rn(O0 / L, O1 / L);
   }
 }
 
