@@ -39,6 +39,19 @@ __host__ __device__ constexpr int decode_tc_stages(int d) { return 2; }
 // joined at the end).  Four warps run: with one warp per CTA (no waiting for other warps at a
 // tile) 64 sequences take as long, and 1 or 8 take up to twice as long (measured), because the
 // rotation, the copies' issue and the joining are then one warp's work.
+// exp2 of a number that is never above zero here: one instruction (-inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// A pair of 32-bit floats from L2, issued where it stands (the split join issues many before it uses any).
+__device__ __forceinline__ float2 ld_l2_pair(const float *p) {
+  float2 v;
+  asm volatile("ld.global.cg.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 template <int D, int DT_WARPS>
 __global__ void __launch_bounds__(DT_WARPS * 32, D <= 64 ? 5 : 3)
 attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, int qkv_parts,
@@ -270,16 +283,16 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m_run[r], mx[r]);
         moff[r] = m_new == -INFINITY ? 0.f : m_new * scale_log2;
-        alpha[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] * scale_log2 - moff[r]);
+        alpha[r] = m_run[r] == -INFINITY ? 0.f : fast_exp2(m_run[r] * scale_log2 - moff[r]);
         m_run[r] = m_new;
       }
       float sum[2] = {0.f, 0.f};
 #pragma unroll
       for (int n = 0; n < NTW; ++n) {
-        s[n][0] = exp2f(fmaf(s[n][0], scale_log2, -moff[0]));
-        s[n][1] = exp2f(fmaf(s[n][1], scale_log2, -moff[0]));
-        s[n][2] = exp2f(fmaf(s[n][2], scale_log2, -moff[1]));
-        s[n][3] = exp2f(fmaf(s[n][3], scale_log2, -moff[1]));
+        s[n][0] = fast_exp2(fmaf(s[n][0], scale_log2, -moff[0]));
+        s[n][1] = fast_exp2(fmaf(s[n][1], scale_log2, -moff[0]));
+        s[n][2] = fast_exp2(fmaf(s[n][2], scale_log2, -moff[1]));
+        s[n][3] = fast_exp2(fmaf(s[n][3], scale_log2, -moff[1]));
         sum[0] += s[n][0] + s[n][1];
         sum[1] += s[n][2] + s[n][3];
       }
@@ -351,7 +364,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
     float L = 0.f, O = 0.f;
 #pragma unroll
     for (int w = 0; w < DT_WARPS; ++w) {
-      const float f = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - M);
+      const float f = sm_m[w][h] == -INFINITY ? 0.f : fast_exp2(sm_m[w][h] - M);
       L += sm_l[w][h] * f;
       O += sm_o[(size_t)(w * DT_ROWS + h) * D + c] * f;
     }
@@ -396,11 +409,11 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
       float2 ov[JB];
 #pragma unroll
       for (int j = 0; j < JB; ++j)
-        ov[j] = __ldcg(reinterpret_cast<const float2 *>(ws_o + (my_slot0 + min(s0 + j, n_active_last)) * D + c));
+        ov[j] = ld_l2_pair(ws_o + (my_slot0 + min(s0 + j, n_active_last)) * D + c);
       for (int i = tid; i < G * JB; i += DT_WARPS * 32) {
         const int hh = i / JB, j = i % JB;
         const size_t slot0 = ((size_t)b * n_heads + kvh * G + hh) * n_splits;
-        float2 ml = __ldcg(reinterpret_cast<const float2 *>(ws_ml + (slot0 + min(s0 + j, n_active_last)) * 2));
+        float2 ml = ld_l2_pair(ws_ml + (slot0 + min(s0 + j, n_active_last)) * 2);
         if (s0 + j > n_active_last) ml = make_float2(-INFINITY, 0.f);
         s_ml[i] = ml;
       }
@@ -408,7 +421,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
       float Mb = M;
 #pragma unroll
       for (int j = 0; j < JB; ++j) Mb = fmaxf(Mb, s_ml[h * JB + j].x);
-      const float keep = M == -INFINITY ? 0.f : exp2f(M - Mb);      // what was summed so far, to the new maximum
+      const float keep = M == -INFINITY ? 0.f : fast_exp2(M - Mb);      // what was summed so far, to the new maximum
       L *= keep;
       O0 *= keep;
       O1 *= keep;
@@ -416,7 +429,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
 #pragma unroll
       for (int j = 0; j < JB; ++j) {
         const float2 ml = s_ml[h * JB + j];
-        const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - Mb);
+        const float f = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - Mb);
         L += ml.y * f;
         O0 += ov[j].x * f;
         O1 += ov[j].y * f;
