@@ -101,6 +101,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_dependents_launch();
+  if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_q);
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+  }
   if (smem_u32(smem) & 1023u) {                               // swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0 && status) atomicCAS(status, 0, 21);
     return;

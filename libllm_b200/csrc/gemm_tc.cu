@@ -82,7 +82,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 6);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The warp's number comes out of a shuffle so that the compiler knows it is the same in all of
+  // a warp's lanes: the loader's and the issuer's loops then run in all 32 lanes (address and
+  // descriptor arithmetic in the uniform datapath), and only the copy, product and commit
+  // instructions themselves are one lane's.  Issued from inside a one-lane branch, a product cost
+  // about 115 cycles of that lane, more than it takes the tensor core at 16 to 128 tokens.
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   grid_dependents_launch();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -116,28 +121,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ loader
-    if (lane == 0) {
-      // The walk over this CTA's (tile, k block) pairs, one per stage filled.
-      struct Walk {
-        int tile, kb, kb1, tok_tile, row_a, row_b;
-        bool valid;
-      };
-      auto start = [&](Walk &w, int tile) {
-        w.tile = tile;
-        w.valid = tile < n_tiles;
-        if (!w.valid) return;
-        const int part = tile % k_parts, row_tile = tile / (k_parts * tok_tiles);
-        w.tok_tile = (tile / k_parts) % tok_tiles;
-        w.kb = part * kb_per_part;
-        w.kb1 = min(n_kblocks_total, w.kb + kb_per_part);
-        w.row_a = row_tile * ROWS_OUT;
-        w.row_b = SW != 0 ? n_out + w.row_a : w.row_a + 64;
-      };
-      auto next = [&](Walk &w) {
-        if (++w.kb >= w.kb1) start(w, w.tile + gridDim.x);
-      };
-      auto load_w = [&](const Walk &w, int stage) {
-        const unsigned dst = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
+    const bool leader = elect_one();
+    // The walk over this CTA's (tile, k block) pairs, one per stage filled.
+    struct Walk {
+      int tile, kb, kb1, tok_tile, row_a, row_b;
+      bool valid;
+    };
+    auto start = [&](Walk &w, int tile) {
+      w.tile = tile;
+      w.valid = tile < n_tiles;
+      if (!w.valid) return;
+      const int part = tile % k_parts, row_tile = tile / (k_parts * tok_tiles);
+      w.tok_tile = (tile / k_parts) % tok_tiles;
+      w.kb = part * kb_per_part;
+      w.kb1 = min(n_kblocks_total, w.kb + kb_per_part);
+      w.row_a = row_tile * ROWS_OUT;
+      w.row_b = SW != 0 ? n_out + w.row_a : w.row_a + 64;
+    };
+    auto next = [&](Walk &w) {
+      if (++w.kb >= w.kb1) start(w, w.tile + gridDim.x);
+    };
+    auto load_w = [&](const Walk &w, int stage) {
+      const unsigned dst = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
+      if (leader) {
         mbar_expect_tx(bar_full + 8 * stage, S::STAGE_BYTES);
         if (SW == 2) {                    // 128 gate rows, then 128 up rows
           tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
@@ -148,83 +154,87 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
           tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
         }
-      };
-      auto load_x = [&](const Walk &w, int stage) {
+      }
+    };
+    auto load_x = [&](const Walk &w, int stage) {
+      if (leader)
         tma_load_2d(smem_u32(smem + (size_t)stage * S::STAGE_BYTES) + S::A_BYTES, &map_x, w.kb * TC_BK,
                     w.tok_tile * TN, bar_full + 8 * stage);
-      };
-      // Weights first: they do not depend on the kernel before this one, so the whole ring
-      // is filled with them while that kernel still runs.  Then the wait, then the tokens of
-      // the same stages, then the rest of the walk stage by stage.
-      Walk w, w2;
-      start(w, blockIdx.x);
-      int n_pre = 0;
-      for (; w.valid && n_pre < STAGES; next(w), ++n_pre) load_w(w, n_pre);
-      grid_dependency_wait();
-      start(w2, blockIdx.x);
-      for (int s = 0; s < n_pre; ++s, next(w2)) load_x(w2, s);
-      int stage = n_pre % STAGES;
-      unsigned phase = n_pre == STAGES ? 1u : 0u;
-      bool ok = true;
-      for (; w.valid; next(w)) {
-        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1);
+    };
+    // Weights first: they do not depend on the kernel before this one, so the whole ring
+    // is filled with them while that kernel still runs.  Then the wait, then the tokens of
+    // the same stages, then the rest of the walk stage by stage.
+    Walk w, w2;
+    start(w, blockIdx.x);
+    int n_pre = 0;
+    for (; w.valid && n_pre < STAGES; next(w), ++n_pre) load_w(w, n_pre);
+    start(w2, blockIdx.x);
+    grid_dependency_wait();
+    for (int s = 0; s < n_pre; ++s, next(w2)) load_x(w2, s);
+    int stage = n_pre % STAGES;
+    unsigned phase = n_pre == STAGES ? 1u : 0u;
+    bool ok = true;
+    for (; w.valid; next(w)) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1));
+      if (!ok) break;
+      load_w(w, stage);
+      load_x(w, stage);
+      if (++stage == STAGES) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    if (leader && (!ok || *abort_flag)) {
+      // given up: let the loads that are in flight land before the CTA goes away
+      const unsigned long long t0 = globaltimer();
+      for (int s = 0; s < STAGES; ++s)
+        while (!mbar_try(bar_full + 8 * s, 0) && !mbar_try(bar_full + 8 * s, 1) && globaltimer() - t0 < 2000000ull) {
+        }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ tensor-core issue
+    const bool leader = elect_one();
+    constexpr unsigned IDESC = instr_desc(TC_ROWS, TN);
+    int stage = 0;
+    unsigned phase = 0;
+    int iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+      const int part = tile % k_parts;
+      const int kb0 = part * kb_per_part, kb1 = min(n_kblocks_total, kb0 + kb_per_part);
+      const int acc = iter & 1;
+      const unsigned acc_phase = (iter >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2));
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned d_tmem = tmem_base + acc * S::ACC_COLS;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3));
         if (!ok) break;
-        load_w(w, stage);
-        load_x(w, stage);
+        tc_fence_after();
+        const unsigned a_addr = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
+        const unsigned long long a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + S::A_BYTES);
+        const unsigned long long a2_desc = smem_desc(a_addr + TC_A_BYTES);
+        const unsigned first = kb > kb0 ? 1u : 0u;
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < TC_BK / 16; ++kk) {  // 16 k = 32 bytes further along the swizzled row
+            tc_mma(d_tmem, a_desc + (unsigned long long)(kk * 2), b_desc + (unsigned long long)(kk * 2), IDESC,
+                   kk > 0 ? 1u : first);
+            if (SW == 2)                             // the up rows into the accumulator beside
+              tc_mma(d_tmem + TN, a2_desc + (unsigned long long)(kk * 2), b_desc + (unsigned long long)(kk * 2), IDESC,
+                     kk > 0 ? 1u : first);
+          }
+          tc_commit(bar_empty + 8 * stage);          // the stage is free when these products have read it
+        }
+        __syncwarp();
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
-      if (!ok || *abort_flag) {
-        // given up: let the loads that are in flight land before the CTA goes away
-        const unsigned long long t0 = globaltimer();
-        for (int s = 0; s < STAGES; ++s)
-          while (!mbar_try(bar_full + 8 * s, 0) && !mbar_try(bar_full + 8 * s, 1) && globaltimer() - t0 < 2000000ull) {
-          }
-      }
-    } else {
-      grid_dependency_wait();
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ tensor-core issue
-    if (lane == 0) {
-      constexpr unsigned IDESC = instr_desc(TC_ROWS, TN);
-      int stage = 0;
-      unsigned phase = 0;
-      int iter = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
-        const int part = tile % k_parts;
-        const int kb0 = part * kb_per_part, kb1 = min(n_kblocks_total, kb0 + kb_per_part);
-        const int acc = iter & 1;
-        const unsigned acc_phase = (iter >> 1) & 1;
-        ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const unsigned d_tmem = tmem_base + acc * S::ACC_COLS;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3);
-          if (!ok) break;
-          tc_fence_after();
-          const unsigned a_addr = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
-          const unsigned long long a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + S::A_BYTES);
-#pragma unroll
-          for (int kk = 0; kk < TC_BK / 16; ++kk) {  // 16 k = 32 bytes further along the swizzled row
-            tc_mma(d_tmem, a_desc + (unsigned long long)(kk * 2), b_desc + (unsigned long long)(kk * 2), IDESC,
-                   (kb > kb0 || kk > 0) ? 1u : 0u);
-            if (SW == 2)                             // the up rows into the accumulator beside
-              tc_mma(d_tmem + TN, smem_desc(a_addr + TC_A_BYTES) + (unsigned long long)(kk * 2),
-                     b_desc + (unsigned long long)(kk * 2), IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
-          }
-          tc_commit(bar_empty + 8 * stage);          // the stage is free when these products have read it
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-        if (ok) tc_commit(bar_tfull + 8 * acc);      // the tile's accumulator is complete
-      }
+      if (ok && leader) tc_commit(bar_tfull + 8 * acc);      // the tile's accumulator is complete
+      __syncwarp();
     }
     grid_dependency_wait();
   } else {

@@ -66,6 +66,17 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// One lane of a converged warp (the same one every time for the full mask).
+__device__ __forceinline__ bool elect_one() {
+  unsigned pred;
+  asm volatile("{\n.reg .pred P;\n.reg .b32 r;\nelect.sync r|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
+  return pred != 0;
+}
+// Brings a tensor map into the cache it is read from, so that the first copy that uses it does
+// not wait for the map as well.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(unsigned bar) {
