@@ -99,7 +99,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 7);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // out of a shuffle, so that the compiler knows the number to be the same in all lanes of a warp
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   grid_dependents_launch();
   if (threadIdx.x == 0) {
     tma_prefetch_map(&map_q);
@@ -151,33 +152,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int *pt = page_table + (size_t)b * pt_stride;
 
   if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
+  // The loader's and the issuers' loops run in all lanes of their warps (waits, addresses and
+  // descriptors in the uniform datapath); one elected lane issues the copies, products and commits.
   if (warp == 8) {
     // ------------------------------------------------------------ loader
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(bar_q, S::Q_BYTES);
-      for (int kb = 0; kb < S::KB; ++kb) {
-        tma_load_2d(smem_u32(sQ) + kb * (FT_BM * 128), &map_q, h * D + kb * 64, q0 + r0, bar_q);
-        tma_load_2d(smem_u32(sQ) + kb * (FT_BM * 128) + 64 * 128, &map_q, h * D + kb * 64, q0 + r0 + 64, bar_q);
+    const bool leader = elect_one();
+    if (n_tiles > 0) {
+      if (leader) {
+        mbar_expect_tx(bar_q, S::Q_BYTES);
+        for (int kb = 0; kb < S::KB; ++kb) {
+          tma_load_2d(smem_u32(sQ) + kb * (FT_BM * 128), &map_q, h * D + kb * 64, q0 + r0, bar_q);
+          tma_load_2d(smem_u32(sQ) + kb * (FT_BM * 128) + 64 * 128, &map_q, h * D + kb * 64, q0 + r0 + 64, bar_q);
+        }
       }
       int stage = 0;
       unsigned phase = 0;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 11);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 11));
         if (!ok) break;
         const int row = (pt[first_tile + j] * n_kv + kvh) * FT_BN;
         const unsigned dk = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES), dv = dk + S::KV_BYTES;
-        mbar_expect_tx(bar_full + 8 * stage, 2 * S::KV_BYTES);
-        for (int kb = 0; kb < S::KB; ++kb) {
-          tma_load_2d(dk + kb * (FT_BN * 128), &map_k, kb * 64, row, bar_full + 8 * stage);
-          tma_load_2d(dv + kb * (FT_BN * 128), &map_v, kb * 64, row, bar_full + 8 * stage);
+        if (leader) {
+          mbar_expect_tx(bar_full + 8 * stage, 2 * S::KV_BYTES);
+          for (int kb = 0; kb < S::KB; ++kb) {
+            tma_load_2d(dk + kb * (FT_BN * 128), &map_k, kb * 64, row, bar_full + 8 * stage);
+            tma_load_2d(dv + kb * (FT_BN * 128), &map_v, kb * 64, row, bar_full + 8 * stage);
+          }
         }
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
-      if (!ok || *abort_flag) {
+      if (leader && (!ok || *abort_flag)) {
         const unsigned long long t0 = globaltimer();
         for (int s = 0; s < STAGES; ++s)
           while (!mbar_try(bar_full + 8 * s, 0) && !mbar_try(bar_full + 8 * s, 1) && globaltimer() - t0 < 2000000ull) {
@@ -186,50 +194,59 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------ tensor-core issue: scores
-    // The two products have an issuing thread each: what a thread spends on an instruction
-    // (descriptors, the hand-over to the tensor core) is more than the instruction takes to run.
-    if (lane == 0 && n_tiles > 0) {
+    // The two products have an issuing warp each.
+    const bool leader = elect_one();
+    if (n_tiles > 0) {
       constexpr unsigned IDESC_S = instr_desc(FT_BM, FT_BN);          // S[128 x 64 keys], both operands K-major
-      bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(bar_q, 0, abort_flag, status, 12));
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int stage = j % STAGES;
         ok = mbar_wait(bar_full + 8 * stage, (j / STAGES) & 1, abort_flag, status, 13);
         // buffer j & 1 last held the scores of tile j - 2 and then its probabilities, which the
-        // other thread's product has to have read
+        // other warp's product has to have read
         if (ok && j >= 2) ok = mbar_wait(bar_pvdone + 8 * (j & 1), ((j >> 1) - 1) & 1, abort_flag, status, 14);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const unsigned ka = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES);
+        if (leader) {
 #pragma unroll
-        for (int kb = 0; kb < S::KB; ++kb)
+          for (int kb = 0; kb < S::KB; ++kb)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            tc_mma(tmem_s + (j & 1) * FT_BN, smem_desc(smem_u32(sQ) + kb * (FT_BM * 128) + kk * 32),
-                   smem_desc(ka + kb * (FT_BN * 128) + kk * 32), IDESC_S, (kb > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(bar_sfull + 8 * (j & 1));
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma(tmem_s + (j & 1) * FT_BN, smem_desc(smem_u32(sQ) + kb * (FT_BM * 128) + kk * 32),
+                     smem_desc(ka + kb * (FT_BN * 128) + kk * 32), IDESC_S, (kb > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar_sfull + 8 * (j & 1));
+        }
+        __syncwarp();
       }
     }
   } else if (warp == 10) {
     // ------------------------------------------------------------ tensor-core issue: output
-    if (lane == 0 && n_tiles > 0) {
+    const bool leader = elect_one();
+    if (n_tiles > 0) {
       constexpr unsigned IDESC_O = instr_desc_mn(FT_BM, D);           // O[128 x D channels], V MN-major
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int stage = j % STAGES;
         ok = mbar_wait(bar_full + 8 * stage, (j / STAGES) & 1, abort_flag, status, 15) &&
              mbar_wait(bar_pfull, j & 1, abort_flag, status, 16);   // and the output row rescaled, if it had to be
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const unsigned va = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES) + S::KV_BYTES;
         // 16 keys to a product: 8 columns of P (it lies over the scores' first columns), 16 rows of
         // V; all D channels at once, the second block of 64 channels FT_BN rows further on
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < FT_BN / 16; ++kk)
-          tc_mma_ts(tmem_o, tmem_s + (j & 1) * FT_BN + kk * 8, smem_desc_lbo(va + kk * 2048, FT_BN * 128), IDESC_O,
-                    (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(bar_ofull);
-        tc_commit(bar_pvdone + 8 * (j & 1));
-        tc_commit(bar_empty + 8 * stage);
+          for (int kk = 0; kk < FT_BN / 16; ++kk)
+            tc_mma_ts(tmem_o, tmem_s + (j & 1) * FT_BN + kk * 8, smem_desc_lbo(va + kk * 2048, FT_BN * 128), IDESC_O,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar_ofull);
+          tc_commit(bar_pvdone + 8 * (j & 1));
+          tc_commit(bar_empty + 8 * stage);
+        }
+        __syncwarp();
       }
     }
   } else if (warp < 8) {
