@@ -92,11 +92,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char *sQ = smem, *sKV = smem + S::Q_BYTES;
   float *xch = reinterpret_cast<float *>(sKV + (size_t)STAGES * 2 * S::KV_BYTES);       // [2][2][128]
   unsigned long long *bars = (unsigned long long *)(xch + 4 * FT_BM);
-  // full[STAGES], empty[STAGES], q_full, s_full[2] (one per score buffer), p_full, o_full, pv_done[2]
+  // full[STAGES], empty[STAGES], q_full, s_full[2], p_full[2] (one per score buffer each), o_full, pv_done[2]
   const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
   const unsigned bar_q = smem_u32(bars + 2 * STAGES), bar_sfull = bar_q + 8,
-                 bar_pfull = bar_q + 24, bar_ofull = bar_q + 32, bar_pvdone = bar_q + 40;
-  unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 7);
+                 bar_pfull = bar_q + 24, bar_ofull = bar_q + 40, bar_pvdone = bar_q + 48;
+  unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 9);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   // out of a shuffle, so that the compiler knows the number to be the same in all lanes of a warp
@@ -120,6 +120,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(bar_sfull, 1);
     mbar_init(bar_sfull + 8, 1);
     mbar_init(bar_pfull, 8);
+    mbar_init(bar_pfull + 8, 8);
     mbar_init(bar_ofull, 1);
     mbar_init(bar_pvdone, 1);
     mbar_init(bar_pvdone + 8, 1);
@@ -151,9 +152,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int n_tiles = last_tile - first_tile + 1;             // <= 0: nothing to do
   const int *pt = page_table + (size_t)b * pt_stride;
 
-  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
   // The loader's and the issuers' loops run in all lanes of their warps (waits, addresses and
-  // descriptors in the uniform datapath); one elected lane issues the copies, products and commits.
+  // descriptors in the uniform datapath); lane 0 issues the copies, products and commits.
+  // Everything the third warpgroup runs stands behind its release of registers, so that the
+  // compiler holds that code to what is left (what it used beyond would be the row threads' by then).
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
   if (warp == 8) {
     // ------------------------------------------------------------ loader
     const bool leader = elect_one();
@@ -230,7 +234,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int stage = j % STAGES;
         ok = mbar_wait(bar_full + 8 * stage, (j / STAGES) & 1, abort_flag, status, 15) &&
-             mbar_wait(bar_pfull, j & 1, abort_flag, status, 16);   // and the output row rescaled, if it had to be
+             mbar_wait(bar_pfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, status, 16);   // and the output row rescaled, if it had to be
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -249,7 +253,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         __syncwarp();
       }
     }
-  } else if (warp < 8) {
+  }
+  } else {
     // ------------------------------------------------------------ two threads per query row
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(S::REGS_MANY));
     const int quarter = warp & 3, half = warp >> 2;
@@ -344,11 +349,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       const float2 sum2 = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
       l_run += sum2.x + sum2.y;
+      // The probabilities' barrier is one per score buffer: a pair of warps may be a tile ahead of
+      // the others (nothing holds it back but the scores), and on a single barrier its arrival for
+      // the next tile would complete this tile's phase in a slower warp's place.
       tc_st16(s_addr + half * 16, pk);
       tc_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull);
+      if (lane == 0) mbar_arrive(bar_pfull + 8 * (j & 1));
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull, (n_tiles - 1) & 1, abort_flag, status, 20));
     // The row's sum is the two threads' sums, first half first.  Every row warp comes here, whatever
