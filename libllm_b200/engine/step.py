@@ -14,6 +14,7 @@ copied into the graph's fixed buffer before each replay."""
 from __future__ import annotations
 
 import gc
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -125,6 +126,11 @@ class Engine:
                                for _ in range(4)]
         self._token_turn = 0
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        # Prompt steps whose shape comes back (batches of equal prompts, a benchmark's repetitions)
+        # are captured too, from their second occurrence on; a few are kept, the oldest goes.
+        self._prompt_graphs: "OrderedDict[tuple, _StepGraph]" = OrderedDict()
+        self._prompt_seen: Dict[tuple, int] = {}
+        self.max_prompt_graphs = 4
         self._eager_desc: Dict[tuple, _Descriptor] = {}
         self.launch_log: Optional[List[str]] = None
         self.steps_run = 0
@@ -162,9 +168,12 @@ class Engine:
         self.cache.reserve({it.slot: self.cache.length(it.slot) + len(it.tokens) for it in items})
 
         decode_only = all(len(it.tokens) == 1 for it in items)
+        out = None
         if decode_only and self.use_graphs and len(items) <= self.max_step_tokens:
             out = self._run_decode_graph(items, sampling, uniforms, return_logits)
-        else:
+        elif self.use_graphs:
+            out = self._run_prompt_graph(items, sampling, uniforms, return_logits)     # None: not this time
+        if out is None:
             out = self._run_eager(items, sampling, uniforms, return_logits)
         self.steps_run += 1
         return out
@@ -378,6 +387,53 @@ class Engine:
         return (logits if return_logits else None), tokens
 
 
+    # ---------------------------------------------------------------- graph path (prompts whose shape repeats)
+    def _run_prompt_graph(self, items, sampling, uniforms, return_logits):
+        """A prompt step as a graph replay, or None when it is to run eagerly: the step must fit one
+        launch sequence, want few places, and have a shape that was seen before.  The shape is
+        what the launches depend on: tokens and sequences in the step, places wanted, the page
+        tables' width and the longest prompt rounded up to the attention kernel's tile of rows.
+        Which sequence has how many tokens, and where they stand, is in the descriptor."""
+        T = sum(len(it.tokens) for it in items)
+        n_want = sum(len(it.want) for it in items)
+        if T > self.max_step_tokens or n_want == 0 or n_want > 64 or len(items) > 1024:
+            return None
+        pieces = [_Piece(i, it.slot, 0, len(it.tokens), self.cache.length(it.slot)) for i, it in enumerate(items)]
+        need_pages = max((p.past + p.count + self.page_size - 1) // self.page_size for p in pieces)
+        width = 8
+        while width < need_pages:
+            width *= 2
+        max_q = (max(p.count for p in pieces) + 127) // 128 * 128
+        key = (T, len(items), n_want, width, max_q, sampling)
+        graph = self._prompt_graphs.get(key)
+        if graph is None:
+            seen = self._prompt_seen.get(key, 0) + 1
+            if len(self._prompt_seen) > 4096:
+                self._prompt_seen.clear()
+            self._prompt_seen[key] = seen
+            if seen < 2:
+                return None
+            while len(self._prompt_graphs) >= self.max_prompt_graphs:
+                torch.cuda.synchronize()
+                self._prompt_graphs.popitem(last=False)
+            graph = self._prompt_graphs[key] = _StepGraph(self, T, len(items), n_want, width, max_q, sampling)
+        else:
+            self._prompt_graphs.move_to_end(key)
+        want_rows, o = [], 0
+        for p in pieces:
+            want_rows.extend(o + w for w in items[p.index].want)
+            o += p.count
+        self._fill(graph.desc, pieces, items, want_rows, list(uniforms) if sampling is not None else None)
+        graph.run()
+        for p in pieces:
+            self.cache.commit(p.slot, p.past + p.count)
+        # a prompt step's results are the caller's own (as the eager path's are): not the graph's buffers
+        logits = graph.logits.clone() if (return_logits or sampling is None) else None
+        if sampling is None:
+            return logits
+        return logits, graph.tokens.clone()
+
+
 class PendingTokens:
     """Tokens of a step on their way from the device to the host."""
 
@@ -389,24 +445,29 @@ class PendingTokens:
         return self._host[:self.n].tolist()
 
 
-class _DecodeGraph:
-    """A captured step of B sequences bringing one token each, page tables ``width`` wide."""
+class _StepGraph:
+    """A captured step of T tokens of B sequences with ``n_want`` wanted places, page tables
+    ``width`` wide and no sequence bringing more than ``max_q`` tokens."""
 
-    def __init__(self, engine: Engine, B: int, width: int, sampling: Optional[SamplingParams]):
-        self.engine, self.B, self.width, self.sampling = engine, B, width, sampling
-        self.desc = _Descriptor(engine.device, B, B, B, [width] * len(engine.cache.groups))
+    def __init__(self, engine: Engine, T: int, B: int, n_want: int, width: int, max_q: int,
+                 sampling: Optional[SamplingParams], decode_only: bool = False):
+        self.engine, self.T, self.B, self.n_want, self.width, self.max_q = engine, T, B, n_want, width, max_q
+        self.sampling, self.decode_only = sampling, decode_only
+        self.desc = _Descriptor(engine.device, T, B, n_want, [width] * len(engine.cache.groups))
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.tokens: Optional[torch.Tensor] = None
 
     def _body(self):
         eng = self.engine
+        # stand-in pieces: the launches depend on the step's shape alone
         pieces = [_Piece(i, 0, 0, 1, 0) for i in range(self.B)]
-        ctx, tables = eng._context(self.desc, pieces, self.B, True, self.width * eng.page_size)
+        ctx, tables = eng._context(self.desc, pieces, self.n_want, self.decode_only, self.width * eng.page_size)
+        ctx.max_q_len = self.max_q
         logits = eng.model.forward(ctx, eng.cache, tables)
         tokens = None
         if self.sampling is not None:
-            tokens = eng._sample(logits, self.sampling, ctx.extras["uniforms"], into_last=True)
+            tokens = eng._sample(logits, self.sampling, ctx.extras["uniforms"], into_last=self.decode_only)
         return logits, tokens
 
     def run(self) -> None:
@@ -439,3 +500,10 @@ class _DecodeGraph:
             return
         self.graph.replay()
         self.logits, self.tokens = self._static
+
+
+class _DecodeGraph(_StepGraph):
+    """A captured step of B sequences bringing one token each, page tables ``width`` wide."""
+
+    def __init__(self, engine: Engine, B: int, width: int, sampling: Optional[SamplingParams]):
+        super().__init__(engine, B, B, B, width, 1, sampling, decode_only=True)
