@@ -5,7 +5,7 @@ first tokens of a sequence."""
 import pytest
 
 import plain_llama as P
-from helpers import check_against_plain, model_folder, plain_weights, tokens_for
+from helpers import check_against_plain, check_logits, model_folder, plain_weights, tokens_for
 from replay import replay_batch
 
 pytestmark = pytest.mark.gpu
@@ -134,3 +134,40 @@ def test_errors_leave_the_cache_unchanged():
     engine.close_sequence(s2)
     with pytest.raises(CacheError):
         engine.close_sequence(s2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_steps_of_a_repeating_shape_are_captured_and_stay_right(dtype):
+    """A prompt step is captured as a graph the second time its shape comes (tokens, sequences,
+    wanted places, table width, longest prompt rounded to 128).  Batches of the same shape but with
+    the tokens spread differently over the sequences, standing behind different numbers of cached
+    tokens, must come out of the eager run, the capturing run and the replays alike; more shapes
+    than the engine keeps graphs for push the oldest out without harm."""
+    from libllm_b200.engine import StepItem
+    engine, c, w = setup("B", dtype, max_tokens=8192)
+    engine._prompt_graphs.clear()
+    engine._prompt_seen.clear()
+    rounds = [([20, 50, 7], 0), ([7, 20, 50], 0), ([30, 30, 17], 0), ([50, 7, 20], 0), ([25, 26, 26], 0)]
+    for r, (lens, _) in enumerate(rounds):
+        seqs = [tokens_for("B", n, 100 + 10 * r + i) for i, n in enumerate(lens)]
+        slots = [engine.open_sequence() for _ in seqs]
+        logits = engine.step([StepItem(s, t, [0, len(t) - 1]) for s, t in zip(slots, seqs)])
+        # a second step of the same sequences, eight tokens each behind what is cached now
+        more = [tokens_for("B", 8, 500 + 10 * r + i) for i in range(len(seqs))]
+        logits2 = engine.step([StepItem(s, t, [7]) for s, t in zip(slots, more)])
+        for s in slots:
+            engine.close_sequence(s)
+        for i, t in enumerate(seqs):
+            ref = plain(c, w, t + more[i])
+            check_logits(logits[2 * i:2 * i + 2].cpu(), ref[[0, len(t) - 1]], dtype, f"round {r} sequence {i}")
+            check_logits(logits2[i:i + 1].cpu(), ref[[len(t) + 7]], dtype, f"round {r} sequence {i}, second step")
+    assert len(engine._prompt_graphs) == 2          # the 77-token shape and the 24-token shape
+    # more shapes than graphs are kept for
+    for n in range(40, 40 + engine.max_prompt_graphs + 2):
+        for rep in range(3):
+            t = tokens_for("B", n, 900 + n)
+            s = engine.open_sequence()
+            got = engine.step([StepItem(s, t, [n - 1])])
+            engine.close_sequence(s)
+            check_logits(got.cpu(), plain(c, w, t)[[n - 1]], dtype, f"length {n} run {rep}")
+    assert len(engine._prompt_graphs) == engine.max_prompt_graphs
