@@ -131,6 +131,7 @@ class Engine:
         self._prompt_graphs: "OrderedDict[tuple, _StepGraph]" = OrderedDict()
         self._prompt_seen: Dict[tuple, int] = {}
         self.max_prompt_graphs = 4
+        self.prompt_graph_max_tokens = 2048      # longer steps gain nothing that pays for the capture
         self._eager_desc: Dict[tuple, _Descriptor] = {}
         self.launch_log: Optional[List[str]] = None
         self.steps_run = 0
@@ -389,14 +390,16 @@ class Engine:
 
     # ---------------------------------------------------------------- graph path (prompts whose shape repeats)
     def _run_prompt_graph(self, items, sampling, uniforms, return_logits):
-        """A prompt step as a graph replay, or None when it is to run eagerly: the step must fit one
-        launch sequence, want few places, and have a shape that was seen before.  The shape is
+        """A prompt step as a graph replay, or None when it is to run eagerly: the step must be short
+        (the host issues a step's 130-odd launches in 2 to 4 ms, which is what a graph saves; a
+        capture costs 30 to 50 ms, and hundreds where its buffers are gigabytes), want few places,
+        and have a shape that was seen before.  The shape is
         what the launches depend on: tokens and sequences in the step, places wanted, the page
         tables' width and the longest prompt rounded up to the attention kernel's tile of rows.
         Which sequence has how many tokens, and where they stand, is in the descriptor."""
         T = sum(len(it.tokens) for it in items)
         n_want = sum(len(it.want) for it in items)
-        if T > self.max_step_tokens or n_want == 0 or n_want > 64 or len(items) > 1024:
+        if T > min(self.max_step_tokens, self.prompt_graph_max_tokens) or n_want == 0 or n_want > 64 or len(items) > 1024:
             return None
         pieces = [_Piece(i, it.slot, 0, len(it.tokens), self.cache.length(it.slot)) for i, it in enumerate(items)]
         need_pages = max((p.past + p.count + self.page_size - 1) // self.page_size for p in pieces)
@@ -488,7 +491,6 @@ class _StepGraph:
             # engine dropped earlier (graphs, events, pinned buffers), and a call such as a free
             # from a destructor invalidates the capture.
             gc_was_on = gc.isenabled()
-            gc.collect()
             gc.disable()
             try:
                 with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
