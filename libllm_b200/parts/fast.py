@@ -184,7 +184,9 @@ def attention(ctx, q: torch.Tensor, cache, spec, scale: float) -> Optional[torch
         return ops.attention_decode(q, out, cache.k, cache.v, ctx.tok_pos, cache.page_table, spec.n_heads,
                                     spec.n_kv_heads, spec.head_dim, cache.page_size, chunk, n_splits, spec.window,
                                     scale, ws_o, ws_ml)
-    if ENABLED["prefill_attention_tc"] and ops.attention_prefill_tc_supported(spec.head_dim, cache.page_size):
+    # (the head sizes are asked here first: asking the library would compile it for a model that never uses it)
+    if ENABLED["prefill_attention_tc"] and spec.head_dim in (64, 128) and \
+            ops.attention_prefill_tc_supported(spec.head_dim, cache.page_size):
         out = torch.empty((ctx.n_tokens, spec.n_heads * spec.head_dim), dtype=q.dtype, device=q.device)
         return ops.attention_prefill_tc(q, out, cache.k, cache.v, ctx.seq_start, ctx.seq_past, cache.page_table,
                                         ctx.n_seqs, ctx.max_q_len, spec.n_heads, spec.n_kv_heads, spec.head_dim,
