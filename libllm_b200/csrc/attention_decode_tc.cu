@@ -133,7 +133,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
     const int page = s_pages[pos / DT_BN - first_tile];
     new_dst = (((size_t)page * n_kv + kvh) * DT_BN + (pos % DT_BN)) * D;
   }
-  constexpr int MAXP = 4;
+  constexpr int MAXP = 8;
   const bool vec = rot_dim == D && qkv_parts <= MAXP && (qkv_stride % 4 == 0) && (qkv_part_stride % 4 == 0) &&
                    ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)table % 16 == 0);
   if (vec) {

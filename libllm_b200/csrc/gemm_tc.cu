@@ -373,8 +373,14 @@ LLM_EXPORT int llm_gemm_tc_suggest_parts(int M, int N, int K) {
   const int tok_tiles = M <= 256 ? 1 : (M + 255) / 256;
   const int tiles = ((N + 127) / 128) * tok_tiles;
   const int kblocks = (K + TC_BK - 1) / TC_BK;
+  // the most parts (up to 8) that still leave every SM at most one tile and every part at least
+  // four K blocks, none of them empty
+  const int most = sm_count() / (tiles > 0 ? tiles : 1) < 8 ? sm_count() / (tiles > 0 ? tiles : 1) : 8;
   int parts = 1;
-  while (parts < 8 && tiles * parts * 2 <= sm_count() && kblocks / (parts * 2) >= 4) parts *= 2;
+  for (int p = 2; p <= most; ++p) {
+    const int per = (kblocks + p - 1) / p;
+    if (per >= 4 && (p - 1) * per < kblocks) parts = p;
+  }
   return parts;
 }
 
