@@ -49,6 +49,26 @@ LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, co
   return LLM_OK;
 }
 
+// ---------------------------------------------------------------- small copies as kernels
+// n 32-bit words from src to dst, either of which may be pinned host memory (which the device
+// reaches by the same address).  A step's descriptor comes in and its tokens go out this way inside
+// the step's graph: a copy of the copy engine there costs 8 to 15 us of hand-over on either side,
+// a kernel two or three.
+__global__ void copy_words_kernel(const int *__restrict__ src, int *__restrict__ dst, int n) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+LLM_EXPORT int llm_copy_words(const int *src, int *dst, int n, cudaStream_t stream) {
+  if (n == 0) return LLM_OK;
+  LLM_REQUIRE(n > 0 && src != nullptr && dst != nullptr, "copy_words: bad arguments");
+  const int blocks = n <= 1024 ? 1 : (n + 1023) / 1024 > 64 ? 64 : (n + 1023) / 1024;
+  llm_launch(copy_words_kernel, blocks, n < 256 ? 64 : 256, 0, stream, src, dst, n);
+  LLM_CHECK_LAUNCH("copy_words");
+  return LLM_OK;
+}
+
 // ---------------------------------------------------------------- add + rmsnorm
 // For each output row i (source row r = rows ? rows[i] : i):
 //   v = resid[r] + sum_p delta[p][r]      (32-bit; parts added in index order)

@@ -94,6 +94,16 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor,
     return out
 
 
+def copy_words(src: torch.Tensor, dst: torch.Tensor, n: int) -> None:
+    """n 32-bit words from src to dst by a kernel; one of the two may be pinned host memory."""
+    assert src.dtype == torch.int32 and dst.dtype == torch.int32 and src.numel() >= n and dst.numel() >= n
+    assert src.is_contiguous() and dst.is_contiguous()
+    for t in (src, dst):
+        if not (t.is_cuda or t.is_pinned()):
+            raise ExtensionError("copy_words: host memory must be pinned")
+    _call("elementwise", "llm_copy_words", [c_void_p, c_void_p, c_int, c_void_p], _ptr(src), _ptr(dst), int(n), _stream())
+
+
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor],
                 eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> None:
     """resid += sum of delta's parts (32-bit, written back unless ``rows`` selects a

@@ -126,6 +126,13 @@ class Engine:
                                for _ in range(4)]
         self._token_turn = 0
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        # A single-token step's graph holds its own copies (descriptor in, tokens out), so a step is one
+        # launch.  Each shape has two graphs taken in turn: while one step runs, the next one's
+        # descriptor is written into the other graph's staging, and a step's tokens are read
+        # while the other graph's step runs.
+        self._graphs_alt: Dict[tuple, "_DecodeGraph"] = {}
+        self._graph_turn: Dict[tuple, int] = {}
+        self._last_decode_graph: Optional["_DecodeGraph"] = None
         # Prompt steps whose shape comes back (batches of equal prompts, a benchmark's repetitions)
         # are captured too, from their second occurrence on; a few are kept, the oldest goes.
         self._prompt_graphs: "OrderedDict[tuple, _StepGraph]" = OrderedDict()
@@ -191,7 +198,12 @@ class Engine:
         n = len(items)
         if n > self.last_tokens.numel():
             raise InvalidArgError(f"step_tokens: {n} sequences, at most {self.last_tokens.numel()} are taken")
+        self._last_decode_graph = None
         _, tokens = self.step(items, sampling, uniforms, return_logits=False)
+        g = self._last_decode_graph
+        if g is not None and g.host_tokens is not None and tokens.data_ptr() == self.last_tokens.data_ptr():
+            # the graph has copied them out itself; its buffer is read before the graph runs again
+            return PendingTokens(n, g.host_tokens, g.desc.copied)
         if tokens.data_ptr() != self.last_tokens.data_ptr():
             self.last_tokens[:n].copy_(tokens)
         host = self._token_buffers[self._token_turn]
@@ -227,7 +239,7 @@ class Engine:
 
     # ---------------------------------------------------------------- descriptor
     def _fill(self, desc: _Descriptor, pieces: List[_Piece], items: Sequence[StepItem],
-              want_rows: List[int], uniforms: Optional[Sequence[float]]) -> None:
+              want_rows: List[int], uniforms: Optional[Sequence[float]], upload: bool = True) -> None:
         desc.wait_host_free()
         tokens, tok_seq, tok_pos = desc.field(0), desc.field(1), desc.field(2)
         seq_start, seq_past, seq_slot = desc.field(3), desc.field(4), desc.field(5)
@@ -254,7 +266,8 @@ class Engine:
         slots = [p.slot for p in pieces]
         for g, w in enumerate(desc.widths):
             desc.field(9 + g).reshape(len(pieces), w)[:] = self.cache.page_table(g, slots, w)
-        desc.upload()
+        if upload:
+            desc.upload()
 
     def _context(self, desc: _Descriptor, pieces: List[_Piece], n_want: int, decode_only: bool,
                  max_kv_len: int) -> Tuple[StepContext, List[torch.Tensor]]:
@@ -365,10 +378,12 @@ class Engine:
         while width < need_pages:
             width *= 2
         key = (B, width, sampling)
-        graph = self._graphs.get(key)
+        turn = self._graph_turn.get(key, 0)
+        self._graph_turn[key] = turn ^ 1
+        table = self._graphs if turn == 0 else self._graphs_alt
+        graph = table.get(key)
         if graph is None:
-            graph = _DecodeGraph(self, B, width, sampling)
-            self._graphs[key] = graph
+            graph = table[key] = _DecodeGraph(self, B, width, sampling)
         # Logits are computed for every sequence; the wanted ones are picked afterwards.
         rows = [i for i, it in enumerate(items) if len(it.want)]
         uni_full = None
@@ -376,8 +391,11 @@ class Engine:
             uni_full = [0.0] * B
             for r, u in zip(rows, uniforms):
                 uni_full[r] = u
-        self._fill(graph.desc, pieces, items, list(range(B)), uni_full)
+        self._fill(graph.desc, pieces, items, list(range(B)), uni_full, upload=False)
         graph.run()
+        graph.desc.copied.record()             # the staging is free, and the tokens are out, when this launch is done
+        graph.desc._pending = True
+        self._last_decode_graph = graph
         for p in pieces:
             self.cache.commit(p.slot, p.past + 1)
         pick = None if len(rows) == B else torch.tensor(rows, device=self.device, dtype=torch.long)
@@ -460,9 +478,14 @@ class _StepGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.tokens: Optional[torch.Tensor] = None
+        # single-token steps carry their copies inside the graph
+        self.host_tokens = (torch.empty(B, dtype=torch.int32, pin_memory=True)
+                            if decode_only and sampling is not None else None)
 
     def _body(self):
         eng = self.engine
+        if self.decode_only:
+            ops.copy_words(self.desc.host, self.desc.dev, self.desc.host.numel())
         # stand-in pieces: the launches depend on the step's shape alone
         pieces = [_Piece(i, 0, 0, 1, 0) for i in range(self.B)]
         ctx, tables = eng._context(self.desc, pieces, self.n_want, self.decode_only, self.width * eng.page_size)
@@ -471,6 +494,8 @@ class _StepGraph:
         tokens = None
         if self.sampling is not None:
             tokens = eng._sample(logits, self.sampling, ctx.extras["uniforms"], into_last=self.decode_only)
+            if self.host_tokens is not None:
+                ops.copy_words(tokens, self.host_tokens, self.B)
         return logits, tokens
 
     def run(self) -> None:
