@@ -610,3 +610,22 @@ def test_attention_prefill_on_tcgen05_with_a_prompt_of_2048_tokens(d, n_heads, n
         for i, r in enumerate(rows):
             ref = P.attention_scores_softmax_values(qs[i:i + 1], ks[0][:r + 1], vs[0][:r + 1], None)
             close(out[r].view(1, n_heads, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
+
+
+def test_copy_words_between_pinned_host_memory_and_the_device():
+    """The small copies inside a single-token step's graph are kernels that read and write pinned
+    host memory directly: both directions, an odd count, and a refusal of pageable memory."""
+    from libllm_b200.csrc import ops
+    from libllm_b200.errors import ExtensionError
+    n = 2353
+    host = torch.arange(n, dtype=torch.int32).pin_memory()
+    dev = torch.full((n + 7,), -1, dtype=torch.int32, device=DEV)
+    ops.copy_words(host, dev, n)
+    torch.cuda.synchronize()
+    assert torch.equal(dev[:n].cpu(), host) and bool((dev[n:] == -1).all())
+    back = torch.zeros(n, dtype=torch.int32).pin_memory()
+    ops.copy_words(dev * 3, back, n)
+    torch.cuda.synchronize()
+    assert torch.equal(back, host * 3)
+    with pytest.raises(ExtensionError):
+        ops.copy_words(torch.zeros(4, dtype=torch.int32), dev, 4)
