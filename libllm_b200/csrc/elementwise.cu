@@ -181,13 +181,22 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
   if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= 8) {
     // one instantiation per bound on the parts: registers for eight parts cost a prompt step
     // (one part, thousands of rows) a third of its speed
-#define ADDNORM_GO(MAXP)                                                                                 \
-  llm_launch(add_rmsnorm_vec_kernel<TD, TO, THREADS, VPT, MAXP>, n_rows, THREADS, 0, stream, resid,      \
+    // A thread per four columns where the row allows it (up to 4,096 columns): with many parts the
+    // loads of a row are in flight from more warps at once.
+#define ADDNORM_GO2(T_, V_, MAXP)                                                                        \
+  llm_launch(add_rmsnorm_vec_kernel<TD, TO, T_, V_, MAXP>, n_rows, T_, 0, stream, resid,                 \
              (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden)
+#define ADDNORM_GO(MAXP)                                                                                 \
+  do {                                                                                                   \
+    if (hidden <= 2048) ADDNORM_GO2(512, 1, MAXP);                                                       \
+    else if (hidden <= 4096) ADDNORM_GO2(1024, 1, MAXP);                                                 \
+    else ADDNORM_GO2(THREADS, VPT, MAXP);                                                                \
+  } while (0)
     if (n_parts <= 1) ADDNORM_GO(1);
     else if (n_parts <= 4) ADDNORM_GO(4);
     else ADDNORM_GO(8);
 #undef ADDNORM_GO
+#undef ADDNORM_GO2
     LLM_CHECK_LAUNCH("add_rmsnorm");
     return LLM_OK;
   }
