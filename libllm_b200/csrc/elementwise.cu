@@ -39,10 +39,16 @@ LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, co
   LLM_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
   LLM_REQUIRE((fed_tokens == nullptr) == (fed_rows == nullptr), "embedding: fed tokens come with their rows");
   int threads = hidden >= 1024 ? 256 : 128;
+  // A step's first kernel after its descriptor has arrived, and launched so that it starts only
+  // when that is complete: the kernels after it read positions and page tables from the descriptor
+  // before they wait for their own predecessors, which is safe because none of them can start before
+  // this one has.  (Inside a single-token step's graph the descriptor comes by a kernel just before
+  // this one; with an overlapping launch here, a later kernel could in rare runs read the positions
+  // of the step before last.)
   if (dtype == LLM_F32)
-    llm_launch(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
+    llm_launch_after(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
   else if (dtype == LLM_BF16)
-    llm_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
+    llm_launch_after(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
   else
     LLM_FAIL("embedding: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("embedding");
@@ -54,10 +60,13 @@ LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, co
 // reaches by the same address).  A step's descriptor comes in and its tokens go out this way inside
 // the step's graph: a copy of the copy engine there costs 8 to 15 us of hand-over on either side,
 // a kernel two or three.
+// The kernels behind it may start only when the words are written: later kernels of a step read
+// the descriptor before they wait for their predecessors.
 __global__ void copy_words_kernel(const int *__restrict__ src, int *__restrict__ dst, int n) {
-  grid_dependents_launch();
   grid_dependency_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
+  __threadfence();
+  grid_dependents_launch();
 }
 
 LLM_EXPORT int llm_copy_words(const int *src, int *dst, int n, cudaStream_t stream) {
