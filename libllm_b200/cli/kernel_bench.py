@@ -195,14 +195,15 @@ def bench_attention_prefill(args, timer):
 
     def fn():
         if use_tc:
-            ops.attention_prefill_tc(q, out, k, v, seq_start, seq_past, table, B, T, nH, nKV, d, 64, None, scale)
+            ops.attention_prefill_tc(q, out, k, v, seq_start, seq_past, table, B, T, nH, nKV, d, 64, None, scale, args.form)
         elif use_fast:
             ops.attention_prefill(q, out, k, v, seq_start, seq_past, table, B, T, nH, nKV, d, 64, None, scale)
         else:
             ops.attention_generic(q, out, k, v, tok_seq, tok_pos, table, nH, nKV, d, 64, None, scale)
     us = timer.run(fn)
     report("attention_prefill_tc" if use_tc else ("attention_prefill" if use_fast else "attention_generic"), us,
-           flops=4 * B * nH * d * T * (T + 1) // 2, batch=B, tokens=T, heads=nH, kv_heads=nKV, head_dim=d)
+           flops=4 * B * nH * d * T * (T + 1) // 2, batch=B, tokens=T, heads=nH, kv_heads=nKV, head_dim=d,
+           **({"form": args.form} if use_tc else {}))
 
 
 def bench_add_rmsnorm(args, timer):
@@ -266,6 +267,8 @@ def main(argv=None) -> int:
     ap.add_argument("--separate", action="store_true",
                     help="attention_decode: time the FMA kernel with its join kernel instead of the fused one")
     ap.add_argument("--mma-sync", action="store_true", help="attention_prefill: time the mma.sync kernel")
+    ap.add_argument("--form", type=int, default=0, choices=[0, 1, 2],
+                    help="attention_prefill on tcgen05: 1 CTAs of 128 rows, 2 of 256 rows, 0 the library's choice")
     ap.add_argument("--generic", action="store_true", help="attention_prefill: time the general kernel")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

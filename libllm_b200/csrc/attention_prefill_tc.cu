@@ -409,11 +409,407 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
+// ------------------------------------------------------------------ the wide form
+// For prompts of more than 128 tokens: one CTA to an SM takes 256 query rows as two tiles of 128, A
+// and B, and tiles of 128 keys (two pages).  Its warps:
+//   warps 0-3 / 4-7   a thread per row of tile A / B with all 128 scores of the row: no partner, no
+//                     exchange of maxima; otherwise as above (lazy exponent reference, P written
+//                     over the scores, the output row in tensor memory);
+//   warp 8            loader: both Q tiles once, then K and V tiles, which serve both query tiles;
+//   warp 9            issues all products, in the order S_A(0) S_B(0), then for every key tile j:
+//                     O_A += P_A(j) V_j, S_A(j+1), O_B += P_B(j) V_j, S_B(j+1).  The tensor core
+//                     works for one query tile while the other's rows compute exponentials.  A
+//                     score buffer needs no second copy: products issued by one thread run in
+//                     order, so S_X(j+1) cannot overtake the product that reads P_X(j).
+// Tensor memory: S_A, S_B (128 columns each), O_A, O_B (D each): all 512 columns at head size 128.
+// At head size 64 there is room for P_A and P_B (64 columns each) beside the scores.  Then the scores
+// of tile j + 1 are asked for as soon as the rows hold tile j's in registers, and are there when the
+// rows come back: what is left of the chain between two tiles of a row is its own work (the products
+// take 770 of 3,400 cycles otherwise, the hand-overs to and from the issuing thread 900).
+// The S product has N = 128 (the tensor core's full rate; N = 64 runs at half), and the fixed costs
+// of a tile (waits, loads from tensor memory, hand-overs) are paid once for 128 keys.
+constexpr int FW_THREADS = 384;
+constexpr int FW_BM = 256;          // query rows per CTA
+constexpr int FW_BN = 128;          // keys per tile = two pages
+
+template <int D>
+struct FwShape {
+  static constexpr int KB = D / 64;
+  static constexpr int Q_BYTES = FW_BM * D * 2;
+  static constexpr int KV_BYTES = FW_BN * D * 2;            // one of K or V
+  static constexpr int STAGES = D == 64 ? 4 : 2;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr size_t SMEM = Q_BYTES + (size_t)STAGES * 2 * KV_BYTES + 256;   // one CTA per SM
+  static constexpr int REGS_LAUNCH = 168, REGS_FEW = 56, REGS_MANY = 216;
+  static_assert(128 * REGS_FEW + 256 * REGS_MANY <= FW_THREADS * REGS_LAUNCH, "register moves must balance within the CTA");
+  static constexpr bool SEP_P = 2 * FW_BN + 2 * (FW_BN / 2) + 2 * D <= TMEM_COLS;    // probabilities beside the scores
+  static constexpr int P_COL = SEP_P ? 2 * FW_BN : 0, P_STEP = SEP_P ? FW_BN / 2 : FW_BN;   // P of query tile x at P_COL + x * P_STEP
+  static constexpr int O_COL = SEP_P ? 3 * FW_BN : 2 * FW_BN;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FW_THREADS, 1)
+attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
+                              long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
+                              const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window,
+                              float scale_log2, int *status) {
+  using S = FwShape<D>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char *sQ = smem, *sKV = smem + S::Q_BYTES;
+  unsigned long long *bars = (unsigned long long *)(sKV + (size_t)STAGES * 2 * S::KV_BYTES);
+  // full[STAGES], empty[STAGES], q_full, then one for each query tile: s_full[2], p_full[2], o_full[2], s_free[2]
+  const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
+  const unsigned bar_q = smem_u32(bars + 2 * STAGES), bar_sfull = bar_q + 8, bar_pfull = bar_q + 24, bar_ofull = bar_q + 40,
+                 bar_sfree = bar_q + 56;
+  unsigned *tmem_slot = (unsigned *)(bars + 2 * STAGES + 9);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+  grid_dependents_launch();
+  if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_q);
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+  }
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, 21);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_q, 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(bar_sfull + 8 * x, 1);
+      mbar_init(bar_pfull + 8 * x, 4);          // the four warps of a query tile
+      mbar_init(bar_ofull + 8 * x, 1);
+      mbar_init(bar_sfree + 8 * x, 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((unsigned)S::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  grid_dependency_wait();
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int q0 = seq_start[b], n_q = seq_start[b + 1] - q0, past = seq_past[b];
+  const int tile = gridDim.x - 1 - blockIdx.x;               // long tiles first
+  const int r0 = tile * FW_BM;
+  const bool active = r0 < n_q;
+  const int rows = active ? min(FW_BM, n_q - r0) : 0;
+  const int kvh = h / (n_heads / n_kv);
+  // Key tiles of the two query tiles: A works on tiles [0, n_a) of the CTA's range, B on [j_b0, n_tiles).
+  const bool has_b = rows > 128;
+  const int first_tile = window > 0 ? max(0, past + r0 - window + 1) / FW_BN : 0;
+  const int n_a = active ? (past + r0 + min(rows, 128) - 1) / FW_BN - first_tile + 1 : 0;
+  const int n_tiles = has_b ? (past + r0 + rows - 1) / FW_BN - first_tile + 1 : n_a;
+  const int j_b0 = has_b ? (window > 0 ? max(0, past + r0 + 128 - window + 1) / FW_BN : 0) - first_tile : n_tiles;
+  const int *pt = page_table + (size_t)b * pt_stride;
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::REGS_FEW));
+  if (warp == 8) {
+    // ------------------------------------------------------------ loader
+    const bool leader = elect_one();
+    if (n_tiles > 0) {
+      if (leader) {
+        mbar_expect_tx(bar_q, S::Q_BYTES);
+        for (int x = 0; x < 2; ++x)
+          for (int kb = 0; kb < S::KB; ++kb)
+            for (int hf = 0; hf < 2; ++hf)
+              tma_load_2d(smem_u32(sQ) + x * (128 * D * 2) + kb * (128 * 128) + hf * (64 * 128), &map_q, h * D + kb * 64,
+                          q0 + r0 + x * 128 + hf * 64, bar_q);
+      }
+      const int last_page = (past + n_q - 1) / 64;            // the sequence's last page with keys
+      int stage = 0;
+      unsigned phase = 0;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 31));
+        if (!ok) break;
+        // A tile's second page may lie behind the sequence's end: the first is loaded in its place
+        // (finite numbers, all masked).
+        const int p0 = 2 * (first_tile + j), p1 = min(p0 + 1, last_page);
+        const int row0 = (pt[p0] * n_kv + kvh) * 64, row1 = (pt[p1] * n_kv + kvh) * 64;
+        const unsigned dk = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES), dv = dk + S::KV_BYTES;
+        if (leader) {
+          mbar_expect_tx(bar_full + 8 * stage, 2 * S::KV_BYTES);
+          for (int kb = 0; kb < S::KB; ++kb) {
+            tma_load_2d(dk + kb * (FW_BN * 128), &map_k, kb * 64, row0, bar_full + 8 * stage);
+            tma_load_2d(dk + kb * (FW_BN * 128) + 64 * 128, &map_k, kb * 64, row1, bar_full + 8 * stage);
+          }
+          for (int kb = 0; kb < S::KB; ++kb) {
+            tma_load_2d(dv + kb * (FW_BN * 128), &map_v, kb * 64, row0, bar_full + 8 * stage);
+            tma_load_2d(dv + kb * (FW_BN * 128) + 64 * 128, &map_v, kb * 64, row1, bar_full + 8 * stage);
+          }
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (leader && (!ok || *abort_flag)) {
+        const unsigned long long t0 = globaltimer();
+        for (int s = 0; s < STAGES; ++s)
+          while (!mbar_try(bar_full + 8 * s, 0) && !mbar_try(bar_full + 8 * s, 1) && globaltimer() - t0 < 2000000ull) {
+          }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ tensor-core issue
+    const bool leader = elect_one();
+    if (n_tiles > 0) {
+      constexpr unsigned IDESC_S = instr_desc(128, FW_BN);            // S[128 rows x 128 keys], both operands K-major
+      constexpr unsigned IDESC_O = instr_desc_mn(128, D);             // O[128 rows x D channels], V MN-major
+      bool ok = __all_sync(0xffffffffu, mbar_wait(bar_q, 0, abort_flag, status, 32));
+      // scores of query tile x against the key tile in `stage`
+      auto scores = [&](int x, int stage) {
+        const unsigned qa = smem_u32(sQ) + x * (128 * D * 2), ka = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES);
+        if (leader) {
+#pragma unroll
+          for (int kb = 0; kb < S::KB; ++kb)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma(tmem_base + x * FW_BN, smem_desc(qa + kb * (128 * 128) + kk * 32),
+                     smem_desc(ka + kb * (FW_BN * 128) + kk * 32), IDESC_S, (kb > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar_sfull + 8 * x);
+        }
+      };
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_full, 0, abort_flag, status, 33));
+      if (ok) {
+        tc_fence_after();
+        scores(0, 0);
+        if (j_b0 == 0) scores(1, 0);
+        __syncwarp();
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int stage = j % STAGES, next_stage = (j + 1) % STAGES;
+        const unsigned va = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES) + S::KV_BYTES;
+        if constexpr (S::SEP_P) {
+          // the next tile's scores first: they need only that the rows hold this tile's in registers
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int c = x ? j - j_b0 : j;
+            const bool act = x ? j >= j_b0 : j < n_a;
+            const bool act_next = j + 1 < n_tiles && (x ? j + 1 >= j_b0 : j + 1 < n_a);
+            if (act_next) {
+              if (act) ok = mbar_wait(bar_sfree + 8 * x, c & 1, abort_flag, status, 40);
+              if (ok) ok = mbar_wait(bar_full + 8 * next_stage, ((j + 1) / STAGES) & 1, abort_flag, status, 35);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              tc_fence_after();
+              scores(x, next_stage);
+            }
+          }
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int c = x ? j - j_b0 : j;                     // how many tiles this query tile has behind it
+          const bool act = x ? j >= j_b0 : j < n_a;
+          const bool act_next = !S::SEP_P && j + 1 < n_tiles && (x ? j + 1 >= j_b0 : j + 1 < n_a);
+          if (act) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_pfull + 8 * x, c & 1, abort_flag, status, 34));   // and the output row rescaled, if it had to be
+            if (!ok) break;
+            tc_fence_after();
+            // 16 keys to a product: 8 columns of P (it lies over the scores' first columns), 16 rows of
+            // V; all D channels at once, the second block of 64 channels a tile's rows further on
+            if (leader) {
+#pragma unroll
+              for (int kk = 0; kk < FW_BN / 16; ++kk)
+                tc_mma_ts(tmem_base + S::O_COL + x * D, tmem_base + S::P_COL + x * S::P_STEP + kk * 8,
+                          smem_desc_lbo(va + kk * 2048, FW_BN * 128), IDESC_O, (c > 0 || kk > 0) ? 1u : 0u);
+              tc_commit(bar_ofull + 8 * x);
+            }
+          }
+          if (act_next) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * next_stage, ((j + 1) / STAGES) & 1, abort_flag, status, 35));
+            if (!ok) break;
+            tc_fence_after();
+            scores(x, next_stage);
+          }
+        }
+        if (!ok) break;
+        if (leader) tc_commit(bar_empty + 8 * stage);
+        __syncwarp();
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------ a thread per query row
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(S::REGS_MANY));
+    const int x = warp >> 2, quarter = warp & 3;
+    const int row = quarter * 32 + lane;                       // row of the query tile = lane of tensor memory
+    const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+    const int pos_lo = past + r0 + x * 128 + quarter * 32;     // the warp's first position
+    const int pos = pos_lo + lane;
+    const unsigned s_addr = tmem_base + x * FW_BN + lane_addr;
+    const unsigned p_addr = tmem_base + S::P_COL + x * S::P_STEP + lane_addr;
+    const unsigned o_addr = tmem_base + S::O_COL + x * D + lane_addr;
+    const int j_lo = x ? j_b0 : 0, j_hi = x ? n_tiles : n_a;
+    float ref = -INFINITY;            // the exponent's reference, already times log2(e) / sqrt(d)
+    float l_run = 0.f;                // sum of the row's exponentials, relative to ref
+    bool ok = j_hi > j_lo;
+    for (int j = j_lo; j < j_hi && ok; ++j) {
+      const int c = j - j_lo;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * x, c & 1, abort_flag, status, 36));
+      if (!ok) break;
+      tc_fence_after();
+      float sc[8][16];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) tc_ld16_issue(s_addr + g * 16, sc[g]);
+      tc_ld_wait();
+#pragma unroll
+      for (int g = 0; g < 8; ++g) tc_ld_ready(sc[g]);
+      if constexpr (S::SEP_P) {                               // the score buffer may be written again
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sfree + 8 * x);
+      }
+      const int k0 = (first_tile + j) * FW_BN;
+      if (k0 + FW_BN - 1 > pos_lo || (window > 0 && k0 <= pos_lo + 31 - window)) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int key = k0 + g * 16 + i;
+            if (!(key <= pos && (window <= 0 || key > pos - window))) sc[g][i] = -INFINITY;
+          }
+      }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], sc[g][i], sc[g][i + 1]);
+      const float mxs = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]) * scale_log2;
+      if (__any_sync(0xffffffffu, mxs > ref + 8.f)) {          // a warp decides as one: the loads below are its own
+        const float new_ref = fmaxf(ref, mxs);
+        const float alpha = new_ref == -INFINITY ? 1.f : fast_exp2(ref - new_ref);
+        if (c > 0) {
+          // the output row may be touched when the tensor core has finished the previous tile's product
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull + 8 * x, (c - 1) & 1, abort_flag, status, 37));
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float t[2][16];
+            tc_ld16_issue(o_addr + c0, t[0]);
+            tc_ld16_issue(o_addr + c0 + 16, t[1]);
+            tc_ld_wait();
+            tc_ld_ready(t[0]);
+            tc_ld_ready(t[1]);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) t[u][i] *= alpha;
+              tc_st16(o_addr + c0 + u * 16, t[u]);
+            }
+          }
+        }
+        l_run *= alpha;
+        ref = new_ref;
+      }
+      const float moff = ref == -INFINITY ? 0.f : ref;
+      float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 scale2 = make_float2(scale_log2, scale_log2), off2 = make_float2(-moff, -moff);
+      // 32 keys at a time: their probabilities, two to a column.  They go over the scores' first
+      // columns at once, or, where they have columns of their own, when the previous tile's output
+      // product has read its probabilities there (it has, as a rule, long before).
+      unsigned pk[4][16];
+#pragma unroll
+      for (int g2 = 0; g2 < 4; ++g2) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          float (&v)[16] = sc[g2 * 2 + u];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), scale2, off2);
+            const float e0 = fast_exp2(t.x), e1 = fast_exp2(t.y);
+            sum4[(i >> 1) & 3] = __fadd2_rn(sum4[(i >> 1) & 3], make_float2(e0, e1));
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+            pk[g2][u * 8 + (i >> 1)] = *reinterpret_cast<const unsigned *>(&b2);
+          }
+        }
+        if constexpr (!S::SEP_P) tc_st16(p_addr + g2 * 16, pk[g2]);
+      }
+      const float2 sum2 = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
+      l_run += sum2.x + sum2.y;
+      if constexpr (S::SEP_P) {
+        if (c > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull + 8 * x, (c - 1) & 1, abort_flag, status, 39));
+          if (!ok) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int g2 = 0; g2 < 4; ++g2) tc_st16(p_addr + g2 * 16, pk[g2]);
+      }
+      tc_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pfull + 8 * x);
+    }
+    if (ok && j_hi > j_lo) ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull + 8 * x, (j_hi - j_lo - 1) & 1, abort_flag, status, 38));
+    if (ok && j_hi > j_lo) {
+      tc_fence_after();
+      const float inv = 1.f / l_run;
+      __nv_bfloat16 *dst = out + (size_t)(q0 + r0 + x * 128 + row) * out_stride + (size_t)h * D;
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float t[2][16];
+        tc_ld16_issue(o_addr + c0, t[0]);
+        tc_ld16_issue(o_addr + c0 + 16, t[1]);
+        tc_ld_wait();
+        tc_ld_ready(t[0]);
+        tc_ld_ready(t[1]);
+        if (x * 128 + row < rows) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int h8 = 0; h8 < 2; ++h8) {
+              uint4 v;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(t[u][h8 * 8] * inv, t[u][h8 * 8 + 1] * inv),
+                             t1 = __floats2bfloat162_rn(t[u][h8 * 8 + 2] * inv, t[u][h8 * 8 + 3] * inv),
+                             t2 = __floats2bfloat162_rn(t[u][h8 * 8 + 4] * inv, t[u][h8 * 8 + 5] * inv),
+                             t3 = __floats2bfloat162_rn(t[u][h8 * 8 + 6] * inv, t[u][h8 * 8 + 7] * inv);
+              v.x = *reinterpret_cast<unsigned *>(&t0);
+              v.y = *reinterpret_cast<unsigned *>(&t1);
+              v.z = *reinterpret_cast<unsigned *>(&t2);
+              v.w = *reinterpret_cast<unsigned *>(&t3);
+              *reinterpret_cast<uint4 *>(dst + c0 + u * 16 + h8 * 8) = v;
+            }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
+                 : "memory");
+  }
+}
+
 template <int D>
 int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out, long long out_stride,
                       const void *kc, const void *vc, long long n_pages, const int *seq_start, const int *seq_past,
                       const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window,
-                      float scale, int *status, cudaStream_t stream) {
+                      float scale, int form, int *status, cudaStream_t stream) {
   using S = FtShape<D>;
   CUtensorMap map_q, map_k, map_v;
   int rc = get_map(q, n_tokens, (long long)n_heads * D, q_stride, 64, &map_q);
@@ -422,6 +818,20 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   if (rc != LLM_OK) return rc;
   rc = get_map(vc, n_pages * n_kv * FT_BN, D, D, 64, &map_v);
   if (rc != LLM_OK) return rc;
+  // Measured: at head size 128 the wide form is ahead from 256 rows on (4 prompts of 2,048: 200 against
+  // 206 us, one of 8,192: 539 against 607); at head size 64 only for long prompts (one of 8,192: 430
+  // against 468 us, 8 of 2,048: 278 against 282, 8 of 512: 46 against 44).
+  if (form == 2 || (form == 0 && max_q_len > (D == 64 ? 1024 : FT_BM))) {
+    using W = FwShape<D>;
+    auto kern = attention_prefill_wide_kernel<D>;
+    LLM_CHECK_CUDA(llm_allow_smem(kern, W::SMEM), "attention_prefill_tc attribute");
+    dim3 grid((max_q_len + FW_BM - 1) / FW_BM, n_heads, n_seqs);
+    LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FW_THREADS), W::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
+                              out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window,
+                              scale * 1.4426950408889634f, status),
+                   "attention_prefill_tc launch");
+    return LLM_OK;
+  }
   auto kern = attention_prefill_tc_kernel<D>;
   LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "attention_prefill_tc attribute");
   dim3 grid((max_q_len + FT_BM - 1) / FT_BM, n_heads, n_seqs);
@@ -442,13 +852,16 @@ LLM_EXPORT int llm_attention_prefill_tc_supports(int d, int page_size) {
 // q [n_tokens, >= heads*d] bfloat16 (rotated; row stride q_stride elements), out [n_tokens, heads*d],
 // caches [n_pages, kv_heads, 64, d]; sequence b owns rows seq_start[b]..seq_start[b+1]-1, which stand at
 // positions seq_past[b].. of the sequence; max_q_len bounds the rows of a sequence.  `status` (device
-// int, may be null) receives a non-zero code if a wait inside the kernel ran out of time.
+// int, may be null) receives a non-zero code if a wait inside the kernel ran out of time.  `form`: 0 the
+// library chooses (the wide form when a sequence brings more than 128 rows), 1 CTAs of 128 rows, 2 of 256.
 LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out,
                                         long long out_stride, const void *kc, const void *vc, long long n_pages,
                                         const int *seq_start, const int *seq_past, const int *page_table,
                                         int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                                        int page_size, int window, float scale, int *status, cudaStream_t stream) {
+                                        int page_size, int window, float scale, int form, int *status,
+                                        cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
+  LLM_REQUIRE(form >= 0 && form <= 2, "attention_prefill_tc: form %d is not one of 0, 1, 2", form);
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv > 0 && n_heads % n_kv == 0,
               "attention_prefill_tc: bad sizes (%d sequences, %d heads, %d kv heads)", n_seqs, n_heads, n_kv);
   LLM_REQUIRE(llm_attention_prefill_tc_supports(d, page_size),
@@ -459,7 +872,7 @@ LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long 
   LLM_REQUIRE(n_pages * n_kv * FT_BN < (1ll << 31), "attention_prefill_tc: the cache has too many rows for one tensor map");
   if (d == 64)
     return launch_prefill_tc<64>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, scale, status, stream);
+                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, scale, form, status, stream);
   return launch_prefill_tc<128>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, scale, status, stream);
+                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, scale, form, status, stream);
 }

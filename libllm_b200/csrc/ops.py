@@ -450,8 +450,10 @@ def attention_prefill_tc_supported(head_dim: int, page_size: int) -> bool:
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                          seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                          max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                         window: Optional[int], scale: float) -> torch.Tensor:
-    """The same attention as ``attention_prefill`` with both products on tcgen05 (head sizes 64, 128)."""
+                         window: Optional[int], scale: float, form: int = 0) -> torch.Tensor:
+    """The same attention as ``attention_prefill`` with both products on tcgen05 (head sizes 64, 128).
+    ``form``: 1 for CTAs of 128 query rows and tiles of 64 keys, 2 for CTAs of 256 rows and tiles of
+    128 keys, 0 for the library's choice (the second when a sequence brings more than 128 rows)."""
     _on_gpu(q, out, kcache, vcache, seq_start, seq_past, page_table)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == q.shape[0]
@@ -459,8 +461,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     _call("attention_prefill_tc", "llm_attention_prefill_tc",
           [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
           _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
           _ptr(seq_start), _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv,
-          head_dim, page_size, int(window or 0), float(scale), _ptr(tc_status(q.device)), _stream())
+          head_dim, page_size, int(window or 0), float(scale), int(form), _ptr(tc_status(q.device)), _stream())
     return out

@@ -518,7 +518,8 @@ def test_attention_decode_fused(n_heads, n_kv, d, window, chunk, n_splits):
 
 @pytest.mark.parametrize("n_heads,n_kv,d,window", [(32, 8, 64, None), (3, 1, 64, None), (8, 2, 128, None), (2, 2, 64, 64),
                                                      (6, 3, 128, 130), (4, 1, 64, 37)])
-def test_attention_prefill_on_tcgen05(n_heads, n_kv, d, window):
+@pytest.mark.parametrize("form", [1, 2])
+def test_attention_prefill_on_tcgen05(n_heads, n_kv, d, window, form):
     """The tcgen05 kernel on the cases of the mma.sync one: whole prompts, the end of a prompt behind
     cached tokens, tile edges (127, 128, 129 rows), single tokens, windows."""
     from libllm_b200.csrc import ops
@@ -533,7 +534,7 @@ def test_attention_prefill_on_tcgen05(n_heads, n_kv, d, window):
     start, past = prefill_inputs(lens, q_lens)
     assert ops.attention_prefill_tc_supported(d, page)
     ops.attention_prefill_tc(q, out, K, V, start, past, table, B, max(q_lens), n_heads, n_kv, d, page, window,
-                             1 / math.sqrt(d))
+                             1 / math.sqrt(d), form)
     ops.check_tc_status()
     o = 0
     for s, n in enumerate(q_lens):
@@ -542,7 +543,8 @@ def test_attention_prefill_on_tcgen05(n_heads, n_kv, d, window):
         o += n
 
 
-def test_attention_prefill_on_tcgen05_finds_a_far_key_and_respects_the_window_edge():
+@pytest.mark.parametrize("form", [1, 2])
+def test_attention_prefill_on_tcgen05_finds_a_far_key_and_respects_the_window_edge(form):
     from libllm_b200.csrc import ops
     d, page, L = 64, 64, 900
     K, V, table, ks, vs = paged_cache(1, [L], 1, d, page, "bfloat16", 73)
@@ -553,7 +555,7 @@ def test_attention_prefill_on_tcgen05_finds_a_far_key_and_respects_the_window_ed
     start, past = prefill_inputs([L], [L])
     for window, sees in ((None, True), (697, False), (698, True)):
         out = torch.empty((L, d), dtype=torch.bfloat16, device=DEV)
-        ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, 1, 1, d, page, window, 1 / math.sqrt(d))
+        ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, 1, 1, d, page, window, 1 / math.sqrt(d), form)
         ops.check_tc_status()
         ref = P.attention_scores_softmax_values(q.cpu().view(L, 1, d), ks[0], vs[0], window)
         close(out.view(L, 1, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
@@ -563,7 +565,8 @@ def test_attention_prefill_on_tcgen05_finds_a_far_key_and_respects_the_window_ed
 
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("step_nats", [6.5, 2.0, -6.5])
-def test_attention_prefill_on_tcgen05_when_the_maximum_moves_from_tile_to_tile(d, step_nats):
+@pytest.mark.parametrize("form", [1, 2])
+def test_attention_prefill_on_tcgen05_when_the_maximum_moves_from_tile_to_tile(d, step_nats, form):
     """The kernel moves a row's exponent reference only when a tile's maximum exceeds it by 2^8, and
     then rescales the output row in tensor memory.  Random scores settle the reference in the first
     tile; here every 64 keys the scores step up by 6.5 nats (the reference moves in every tile and
@@ -582,14 +585,15 @@ def test_attention_prefill_on_tcgen05_when_the_maximum_moves_from_tile_to_tile(d
         K[int(table[0, lp]), 0, :n] = ks[0][lp * page:lp * page + n, 0].to(DEV)
     start, past = prefill_inputs([L], [L])
     out = torch.full((L, n_heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, n_heads, n_kv, d, page, None, 1 / math.sqrt(d))
+    ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, n_heads, n_kv, d, page, None, 1 / math.sqrt(d), form)
     ops.check_tc_status()
     ref = P.attention_scores_softmax_values(q.cpu().view(L, n_heads, d), ks[0], vs[0], None)
     close(out.view(L, n_heads, d), ref, "bfloat16", scale=max(1.0, float(ref.abs().max())))
 
 
 @pytest.mark.parametrize("d,n_heads,n_kv", [(64, 32, 8), (128, 8, 2)])
-def test_attention_prefill_on_tcgen05_with_a_prompt_of_2048_tokens(d, n_heads, n_kv):
+@pytest.mark.parametrize("form", [1, 2])
+def test_attention_prefill_on_tcgen05_with_a_prompt_of_2048_tokens(d, n_heads, n_kv, form):
     """A prompt as long as the benchmark's: 16 query tiles a head and up to 32 key tiles a CTA, so the
     rings of key/value stages and the two score buffers go round many times, with queries that lie
     strided in the stacked q|k|v rows as the engine has them.  Every 97th row is checked against
@@ -602,7 +606,7 @@ def test_attention_prefill_on_tcgen05_with_a_prompt_of_2048_tokens(d, n_heads, n
     start, past = prefill_inputs([L], [L])
     out = torch.full((L, n_heads * d), float("nan"), dtype=torch.bfloat16, device=DEV)
     for _ in range(3):          # the same launch again: a race shows in some runs only
-        ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, n_heads, n_kv, d, page, None, 1 / math.sqrt(d))
+        ops.attention_prefill_tc(q, out, K, V, start, past, table, 1, L, n_heads, n_kv, d, page, None, 1 / math.sqrt(d), form)
         ops.check_tc_status()
         assert bool(torch.isfinite(out.float()).all())
         rows = list(range(0, L, 97)) + [L - 1]
