@@ -1,6 +1,7 @@
 // Causal grouped-query attention for prompt steps on the 5th-generation tensor cores: the flash
 // form (running maximum and sum per query row, scores never stored) with both products as
-// tcgen05.mma, their accumulators in tensor memory and all operands brought by TMA.
+// tcgen05.mma, their accumulators in tensor memory and all operands brought by TMA.  Two forms: the
+// first, described here, for short prompts; the second ("the wide form", further down) for long ones.
 //
 // One CTA takes 128 query rows of one head of one sequence.  Its warps:
 //   warp 8    one lane loads the Q tile once and then, page by page, the K and V tiles (a page of
