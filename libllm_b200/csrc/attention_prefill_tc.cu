@@ -821,8 +821,9 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   if (rc != LLM_OK) return rc;
   // Measured: at head size 128 the wide form is ahead from 256 rows on (4 prompts of 2,048: 200 against
   // 206 us, one of 8,192: 539 against 607); at head size 64 only for long prompts (one of 8,192: 430
-  // against 468 us, 8 of 2,048: 278 against 282, 8 of 512: 46 against 44).
-  if (form == 2 || (form == 0 && max_q_len > (D == 64 ? 1024 : FT_BM))) {
+  // against 468 us, 8 of 2,048: 278 against 282, 8 of 512: 46 against 44; and inside a whole prompt
+  // step of 2,048 tokens it is 6 us a layer behind, alone on its SM with all of tensor memory).
+  if (form == 2 || (form == 0 && max_q_len > (D == 64 ? 2048 : FT_BM))) {
     using W = FwShape<D>;
     auto kern = attention_prefill_wide_kernel<D>;
     LLM_CHECK_CUDA(llm_allow_smem(kern, W::SMEM), "attention_prefill_tc attribute");
