@@ -9,8 +9,9 @@ position each belongs to, and the kernels index the paged cache with them.  Only
 tokens given are computed; padding does not exist.
 
 Steps in which every sequence brings one token are captured once per batch shape as a
-CUDA graph and replayed; the step's descriptor (tokens, positions, page tables) is
-copied into the graph's fixed buffer before each replay."""
+CUDA graph and replayed; the graph's first kernel brings the step's descriptor (tokens,
+positions, page tables) from pinned host memory into the graph's fixed buffer, its last
+one takes the sampled tokens out.  Prompt steps whose shape comes back are captured too."""
 from __future__ import annotations
 
 import gc
@@ -98,6 +99,11 @@ class _Descriptor:
 
     def upload(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
+        self.in_flight()
+
+    def in_flight(self) -> None:
+        """What was launched up to here reads the host staging (a copy, or a graph that copies
+        by itself): the staging is free again when that has run."""
         self.copied.record()
         self._pending = True
 
@@ -160,7 +166,8 @@ class Engine:
         device tensor [wanted, vocab] in the order of the items and of their ``want``.
         With ``sampling`` it returns (logits or None, tokens): a token drawn at each
         wanted place (int32 on the device); ``uniforms`` then holds one number in [0, 1)
-        per wanted place."""
+        per wanted place.  What a step of single tokens returns lies in its graph's buffers,
+        which the step after next of the same shape writes again: copy what is to be kept."""
         items = list(items)
         if not items:
             raise InvalidArgError("a step needs at least one sequence")
@@ -393,8 +400,7 @@ class Engine:
                 uni_full[r] = u
         self._fill(graph.desc, pieces, items, list(range(B)), uni_full, upload=False)
         graph.run()
-        graph.desc.copied.record()             # the staging is free, and the tokens are out, when this launch is done
-        graph.desc._pending = True
+        graph.desc.in_flight()                 # the staging is free, and the tokens are out, when this launch is done
         self._last_decode_graph = graph
         for p in pieces:
             self.cache.commit(p.slot, p.past + 1)
@@ -404,7 +410,6 @@ class Engine:
             return logits
         tokens = graph.tokens if pick is None else graph.tokens[pick]
         return (logits if return_logits else None), tokens
-
 
     # ---------------------------------------------------------------- graph path (prompts whose shape repeats)
     def _run_prompt_graph(self, items, sampling, uniforms, return_logits):
