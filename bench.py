@@ -6,7 +6,7 @@
 Default run: the layer sizes of Llama-3.2-1B with random bfloat16 weights, a batch of 8
 sequences with 2,048-token prompts in a 4,096-token context; a "step" is one decode
 step of the whole batch.  ``value`` is decoded tokens a second with the step timed on the
-device (CUDA events around K graph replays); ``e2e`` is the same through the Python entry
+device (CUDA events on the engine's stream around K decode steps); ``e2e`` is the same through the Python entry
 point (``Model.generate``), host token ids in and sampled ids out at every step.  The line
 also carries the prefill of 2,048 tokens, the decode step's bytes against the memory
 bandwidth, and decode at batch 1 and 64.  The decode step reads about 3 GB (weights and
@@ -104,58 +104,39 @@ def model_numbers(c):
 
 
 def decode_rate(model, batch, steps, warmup, vocab, seed=0):
-    """Decoded tokens a second at ``batch`` with the step timed on the device."""
+    """Decoded tokens a second at ``batch`` with the steps timed on the device: CUDA events on the
+    engine's stream around ``steps`` decode steps that are queued one behind the other (each takes
+    its tokens from the one before on the device, so nothing waits for the host; the host queues a
+    step in a small part of the time the device takes to run one).  Also returns the kernel
+    launches of one step, counted by the host library while the step's graph was made."""
     import torch
+    from libllm_b200 import _lib
     from libllm_b200.engine import GREEDY, StepItem
     eng = model.engine
+    stream = torch.cuda.ExternalStream(eng.stream)
     g = torch.Generator().manual_seed(seed)
     slots = [eng.open_sequence() for _ in range(batch)]
     try:
         prompts = torch.randint(0, vocab, (batch, PROMPT), generator=g).tolist()
         # prompts in one step (the engine cuts it into launches of max_step_tokens)
-        _, toks = eng.step([StepItem(s, p, [PROMPT - 1]) for s, p in zip(slots, prompts)], GREEDY,
-                           return_logits=False)
-        cur = toks.cpu().tolist()
-        for _ in range(warmup):
-            _, toks = eng.step([StepItem(s, [t], [0]) for s, t in zip(slots, cur)], GREEDY, return_logits=False)
-            cur = toks.cpu().tolist()
-        # the graph that the timed steps replay, and its launch count
-        key = [k for k in eng._graphs if k[0] == batch][-1]
-        graph = eng._graphs[key]
+        eng.step_tokens([StepItem(s, p, [PROMPT - 1]) for s, p in zip(slots, prompts)], GREEDY).result()
+        fed = [StepItem(s, [0], [0], fed_row=i) for i, s in enumerate(slots)]
+        n0 = _lib.lib().llm_kernel_launches()
+        eng.step_tokens(fed, GREEDY).result()          # a shape's first step runs once and is captured once
+        launches = (_lib.lib().llm_kernel_launches() - n0) // 2
+        for _ in range(max(warmup - 1, 2)):
+            eng.step_tokens(fed, GREEDY).result()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(steps):
-            # device-only timing: the same step replayed (tokens and positions as uploaded last)
-            graph.graph.replay()
-        end.record()
-        torch.cuda.synchronize()
+        eng.synchronize()
+        start.record(stream)
+        pending = [eng.step_tokens(fed, GREEDY) for _ in range(steps)]
+        end.record(stream)
+        for p in pending:
+            p.result()
+        eng.synchronize()
         ms = start.elapsed_time(end) / steps
         ctx_len = eng.sequence_length(slots[0])
-        return batch * 1000.0 / ms, ms, ctx_len, graph
-    finally:
-        for s in slots:
-            eng.close_sequence(s)
-
-
-def count_graph_launches(model, batch):
-    """Kernel launches of this library in one decode step of ``batch`` (counted while the
-    step runs outside a graph)."""
-    import torch
-    from libllm_b200.csrc import ops
-    from libllm_b200.engine import GREEDY, StepItem
-    eng = model.engine
-    slots = [eng.open_sequence() for _ in range(batch)]
-    try:
-        eng.step([StepItem(s, [1, 2, 3], []) for s in slots])
-        was = eng.use_graphs
-        eng.use_graphs = False
-        n0 = ops.LAUNCHES[0]
-        eng.step([StepItem(s, [5], [0]) for s in slots], GREEDY, return_logits=False)
-        n = ops.LAUNCHES[0] - n0
-        eng.use_graphs = was
-        torch.cuda.synchronize()
-        return n + 2        # inside its graph the step has two more: the descriptor in, the tokens out
+        return batch * 1000.0 / ms, ms, ctx_len, launches
     finally:
         for s in slots:
             eng.close_sequence(s)
@@ -179,26 +160,26 @@ def e2e_rate(model, batch, steps, warmup, vocab, seed=1):
                    stop_token_ids=[], max_batch=batch, on_token=on_token)
     # stamps[0] follows the prompt step; steps warmup+1 .. warmup+steps are timed
     t = stamps[warmup + steps] - stamps[warmup]
-    graph = [v for k, v in model.engine._graphs.items() if k[0] == batch][-1]
-    h2d = graph.desc.host.numel() * 4
-    return batch * steps / t, h2d, batch * 4
+    info = model.engine.info()
+    return batch * steps / t, info["last_step_h2d_bytes"], info["last_step_d2h_bytes"]
 
 
 def prefill_rate(model, vocab, flops_fn, peak_tflops, reps=3):
     import torch
     from libllm_b200.engine import StepItem
     eng = model.engine
+    stream = torch.cuda.ExternalStream(eng.stream)
     g = torch.Generator().manual_seed(7)
     prompt = torch.randint(0, vocab, (PROMPT,), generator=g).tolist()
     times = []
     for r in range(reps + 2):
         s = eng.open_sequence()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record()
-        eng.step([StepItem(s, prompt, [PROMPT - 1])])
-        b.record()
-        torch.cuda.synchronize()
+        eng.synchronize()
+        a.record(stream)
+        eng.step([StepItem(s, prompt, [PROMPT - 1])])      # returns when the wanted row's logits are in host memory
+        b.record(stream)
+        eng.synchronize()
         eng.close_sequence(s)
         if r >= 2:
             times.append(a.elapsed_time(b))
@@ -316,10 +297,9 @@ def main():
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", **prefill_rate(model, vocab, flops_fn, pk["bf16_tflops"])}))
         return 0
-    launches_per_step = count_graph_launches(model, args.batch)
     sampler = ClockSampler()
     sampler.start()
-    rate, ms, ctx_len, _ = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+    rate, ms, ctx_len, launches_per_step = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
     clocks = sampler.stop()
     e2e, h2d, d2h = e2e_rate(model, args.batch, args.steps, args.warmup, vocab)
     prefill = prefill_rate(model, vocab, flops_fn, pk["bf16_tflops"])

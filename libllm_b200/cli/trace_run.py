@@ -11,7 +11,7 @@ wanted places, in the order of the entries and of ``want``, as little-endian 32-
 floats [wanted, vocab].  After every step ``done <step>`` is printed and flushed.
 
 It samples nothing and has no forward pass, cache or loader of its own: it drives the
-library's model, step function and cache, the ones generation uses.  The reference's
+host library's model, step function and cache (C++), the ones generation uses.  The reference's
 nearest thing is the test that feeds stored token ids and compares stored logits
 (src/libllm/llama_test.cc:143-190) and its token-by-token loop (:211-216)."""
 from __future__ import annotations
@@ -32,13 +32,11 @@ def main(argv=None) -> int:
     ap.add_argument("--no-graphs", action="store_true", help="do not capture single-token steps as CUDA graphs")
     args = ap.parse_args(argv)
 
-    import torch
-    from libllm_b200.engine import Engine, Model, StepItem
+    from libllm_b200.engine import Engine, StepItem
 
     os.makedirs(args.out, exist_ok=True)
-    model = Model.from_folder(args.model, dtype=args.dtype, device="cuda:0",
-                              max_positions=max(64, (args.max_tokens + 63) // 64 * 64))
-    engine = Engine(model, max_tokens=args.max_tokens, use_graphs=not args.no_graphs)
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, use_graphs=not args.no_graphs,
+                                max_seq_len=max(64, (args.max_tokens + 63) // 64 * 64))
     slots = {}
     for line in sys.stdin:
         line = line.strip()
@@ -52,15 +50,13 @@ def main(argv=None) -> int:
                 slots[rid] = engine.open_sequence()
             items.append(StepItem(slots[rid], e["tokens"], e.get("want", [])))
         if items:
-            logits = engine.step(items)
+            logits = engine.step(items)          # float32 [wanted, vocab] in host memory, the step complete
             if logits is not None and logits.shape[0] > 0:
-                data = logits.to(torch.float32).contiguous().cpu().numpy().astype("<f4", copy=False)
                 with open(os.path.join(args.out, f"{rec['step']}.f32"), "wb") as f:
-                    f.write(data.tobytes())
+                    f.write(logits.astype("<f4", copy=False).tobytes())
         for rid in rec.get("end", []):
             if rid in slots:
                 engine.close_sequence(slots.pop(rid))
-        torch.cuda.synchronize()
         print(f"done {rec['step']}", flush=True)
     return 0
 

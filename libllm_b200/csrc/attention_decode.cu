@@ -237,7 +237,9 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
   const int head = blockIdx.x, b = blockIdx.y;
   const int len = tok_pos[b] + 1;
   const int kstart = window > 0 ? max(0, len - window) : 0;
-  const int first = kstart / chunk, last = (len - 1) / chunk;
+  // Splits beyond n_splits do not exist (the caller's n_splits * chunk should cover the longest
+  // sequence; keys beyond it were not attended to): never read another head's scratch.
+  const int first = min(kstart / chunk, n_splits - 1), last = min((len - 1) / chunk, n_splits - 1);
   const size_t slot0 = ((size_t)b * n_heads + head) * n_splits;
   float M = -INFINITY;
   for (int s = first; s <= last; ++s) M = fmaxf(M, ws_ml[(slot0 + s) * 2]);
@@ -347,6 +349,17 @@ LLM_EXPORT int llm_attention_decode_static(const void *q, long long q_stride, vo
               n_seqs, n_heads, n_splits, d, need, (long long)LLM_ATTENTION_DECODE_STATIC_FLOATS);
   float *ws_o = nullptr, *ws_ml = nullptr;
   if (n_splits > 1) {
+    // The array that is looked up is the current device's; a stream of another device would make
+    // the kernels run there with this device's address.
+    if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+      int cur = -1, sdev = -1;
+      LLM_CHECK_CUDA(cudaGetDevice(&cur), "attention_decode_static: cudaGetDevice");
+      if (cudaStreamGetDevice(stream, &sdev) == cudaSuccess)
+        LLM_REQUIRE(sdev == cur, "attention_decode_static: the stream belongs to device %d, the current device is %d; make "
+                    "the stream's device current before the call", sdev, cur);
+      else
+        cudaGetLastError();
+    }
     float *base = nullptr;
     const int rc = static_scratch(&base);
     if (rc != LLM_OK) return rc;

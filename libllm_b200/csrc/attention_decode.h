@@ -9,7 +9,8 @@ extern "C" {
 // Attention of one query token per sequence over the paged bfloat16 cache, keys cut into
 // `n_splits` runs of `chunk`.  The caller brings the scratch through which the splits are joined:
 // ws_o needs n_seqs*n_heads*n_splits*d floats and ws_ml n_seqs*n_heads*n_splits*2 (both may be null
-// when n_splits is 1).  Returns 0 or a status; llm_attention_decode_last_error() has the message.
+// when n_splits is 1).  n_splits * chunk must cover the longest sequence: keys beyond it are not
+// attended to.  Returns 0 or a status; llm_attention_decode_last_error() has the message.
 int llm_attention_decode(const void *q, long long q_stride, void *out, long long out_stride, const void *kc,
                          const void *vc, const int *tok_pos, const int *page_table, int pt_stride, int n_seqs,
                          int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window, float scale,
@@ -32,7 +33,8 @@ int llm_attention_decode(const void *q, long long q_stride, void *out, long long
 //    message that says so, and nothing is launched.  With n_splits == 1 no scratch is used.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
 //    device current) and keeps it.  Make that first call before any stream capture begins on the
-//    device, and from one thread.
+//    device, and from one thread.  The array used is the CURRENT device's: a stream that belongs to
+//    another device is refused (make the stream's device current first).
 //  * All calls share the one array, and it keeps what the last call left in it.  The kernels write
 //    every scratch element they later read, so nothing has to be cleared between calls; but two
 //    calls whose kernels may run at the same time (different streams) would overwrite each other's

@@ -118,12 +118,25 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   // (positions and page tables come from the step's descriptor, copied before the step's first
   // kernel): the first NS tiles are on their way while that kernel, the q|k|v product, still
   // runs.  The new token's row is put into its tile by hand further down.
+  // A run that reads another run's cache (write_cache == 0) finds the new token's row written by
+  // that run's kernel, a few launches earlier in this same step.  Overlapping launches do not
+  // order such a kernel before this one's prologue (each kernel only waits for the one directly
+  // before it), so this form fetches nothing before the wait.
+  if (write_cache) {
 #pragma unroll
-  for (int i = 0; i < NS; ++i) {
-    if (first_tile + i <= last_tile) load_kv(first_tile + i, i);
-    cp_async_commit();
+    for (int i = 0; i < NS; ++i) {
+      if (first_tile + i <= last_tile) load_kv(first_tile + i, i);
+      cp_async_commit();
+    }
   }
   grid_dependency_wait();
+  if (!write_cache) {
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+      if (first_tile + i <= last_tile) load_kv(first_tile + i, i);
+      cp_async_commit();
+    }
+  }
 
   // The group's queries, rotated, as rows of the MMA tile (rows beyond the group are zeros), and
   // the new token's key (rotated) and value: into the cache, and kept for this CTA's own tile.

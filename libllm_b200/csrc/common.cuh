@@ -126,6 +126,18 @@ static inline cudaError_t llm_launch_after(void (*kernel)(KArgs...), dim3 grid, 
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Streaming multiprocessors of the current device (asked once per process).
+static inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -78,6 +78,27 @@ LLM_EXPORT int llm_copy_words(const int *src, int *dst, int n, cudaStream_t stre
   return LLM_OK;
 }
 
+// n1 words from src1 followed by n2 words from src2, to dst (which may be pinned host memory): a
+// step's sampled tokens and the status word of its tensor-core kernels leave the device together.
+__global__ void gather_words_kernel(const int *__restrict__ src1, int n1, const int *__restrict__ src2, int n2,
+                                    int *__restrict__ dst) {
+  grid_dependency_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n1 + n2; i += gridDim.x * blockDim.x)
+    dst[i] = i < n1 ? src1[i] : src2[i - n1];
+  __threadfence_system();
+  grid_dependents_launch();
+}
+
+LLM_EXPORT int llm_gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cudaStream_t stream) {
+  if (n1 + n2 == 0) return LLM_OK;
+  LLM_REQUIRE(n1 >= 0 && n2 >= 0 && dst != nullptr && (n1 == 0 || src1) && (n2 == 0 || src2), "gather_words: bad arguments");
+  const int n = n1 + n2;
+  const int blocks = n <= 1024 ? 1 : (n + 1023) / 1024 > 64 ? 64 : (n + 1023) / 1024;
+  llm_launch(gather_words_kernel, blocks, n < 256 ? 64 : 256, 0, stream, src1, n1, src2, n2, dst);
+  LLM_CHECK_LAUNCH("gather_words");
+  return LLM_OK;
+}
+
 // ---------------------------------------------------------------- add + rmsnorm
 // For each output row i (source row r = rows ? rows[i] : i):
 //   v = resid[r] + sum_p delta[p][r]      (32-bit; parts added in index order)
@@ -283,7 +304,7 @@ LLM_EXPORT int llm_swiglu(int in_dtype, int dtype, const void *gu, void *out, in
   const bool vec = inter % 4 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0;
   const size_t total = vec ? (size_t)n_tokens * (inter / 4) : (size_t)n_tokens * inter;
   size_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
 #define SWIGLU_GO(TI, T)                                                                                     \
   do {                                                                                                       \
     if (vec)                                                                                                 \
@@ -297,5 +318,84 @@ LLM_EXPORT int llm_swiglu(int in_dtype, int dtype, const void *gu, void *out, in
   else LLM_FAIL("swiglu: unsupported dtypes in %d out %d", in_dtype, dtype);
 #undef SWIGLU_GO
   LLM_CHECK_LAUNCH("swiglu");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- scaling of rows and logits
+// x *= scale over n values: the token rows of an architecture that scales its embedding.
+__global__ void scale_rows_kernel(float *__restrict__ x, long long n, float scale) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] *= scale;
+}
+
+LLM_EXPORT int llm_scale_rows(float *x, long long n, float scale, cudaStream_t stream) {
+  if (n == 0) return LLM_OK;
+  LLM_REQUIRE(n > 0 && x != nullptr, "scale_rows: bad arguments");
+  long long blocks = (n + 255) / 256;
+  if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+  llm_launch(scale_rows_kernel, (unsigned)blocks, 256, 0, stream, x, n, scale);
+  LLM_CHECK_LAUNCH("scale_rows");
+  return LLM_OK;
+}
+
+// logit = logit * scale, then, with a positive cap, cap * tanh(logit / cap), in 32-bit.
+__global__ void logit_transform_kernel(float *__restrict__ x, long long n, float scale, float cap) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
+LLM_EXPORT int llm_logit_transform(float *x, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n == 0) return LLM_OK;
+  LLM_REQUIRE(n > 0 && x != nullptr, "logit_transform: bad arguments");
+  long long blocks = (n + 255) / 256;
+  if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+  llm_launch(logit_transform_kernel, (unsigned)blocks, 256, 0, stream, x, n, scale, cap);
+  LLM_CHECK_LAUNCH("logit_transform");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- random weights on the device
+// Element i is a pure function of (seed, i): two SplitMix64 outputs give two uniform numbers;
+// law 0 turns them into a normal number with mean a and deviation b (Box-Muller), law 1 into a
+// uniform number in [a, b).  The random-weights mode of a benchmark fills its tensors here
+// instead of drawing a billion numbers on the host.
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void random_fill_kernel(T *__restrict__ out, long long n, unsigned long long seed, int law, float a, float b) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const unsigned long long h1 = splitmix64(seed ^ splitmix64((unsigned long long)i));
+    const unsigned long long h2 = splitmix64(h1);
+    const float u1 = ((float)(h1 >> 40) + 1.0f) * (1.0f / 16777216.0f);      // (0, 1]
+    const float u2 = (float)(h2 >> 40) * (1.0f / 16777216.0f);               // [0, 1)
+    float v;
+    if (law == 0) v = a + b * sqrtf(-2.0f * logf(u1)) * cosf(6.283185307179586f * u2);
+    else v = a + (b - a) * u2;
+    out[i] = from_float<T>(v);
+  }
+}
+
+LLM_EXPORT int llm_random_fill(void *out, int dtype, long long n, unsigned long long seed, int law, float a, float b,
+                               cudaStream_t stream) {
+  if (n == 0) return LLM_OK;
+  LLM_REQUIRE(n > 0 && out != nullptr && (law == 0 || law == 1), "random_fill: bad arguments");
+  long long blocks = (n + 255) / 256;
+  if (blocks > (long long)sm_count() * 32) blocks = (long long)sm_count() * 32;
+  if (dtype == LLM_F32) random_fill_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>((float *)out, n, seed, law, a, b);
+  else if (dtype == LLM_BF16) random_fill_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((__nv_bfloat16 *)out, n, seed, law, a, b);
+  else LLM_FAIL("random_fill: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("random_fill");
   return LLM_OK;
 }

@@ -411,3 +411,28 @@ LLM_EXPORT int llm_gemm_tc(const void *x, long long ldx, const void *W, void *ou
   }
   LLM_FAIL("gemm_tc: unknown output dtype %d", out_dtype);
 }
+
+// ---------------------------------------------------------------- a wait that runs out, for tests
+// One warp waits, through the same bounded wait as the product's warps, on a barrier that nobody
+// arrives on: no copy and no tensor memory is in flight.  After `limit_ns` the wait gives up,
+// records code 9 in `status` and the kernel returns by itself.  It shows that a wait that runs out
+// leaves the device usable and is seen by the host; nothing else launches it.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int *status) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, status, 9, limit_ns);
+}
+
+LLM_EXPORT int llm_gemm_tc_wait_probe(long long limit_ns, int *status, cudaStream_t stream) {
+  LLM_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ll, "wait_probe: the limit must lie in (0, 100 ms]");
+  LLM_REQUIRE(status != nullptr, "wait_probe: no status word");
+  wait_probe_kernel<<<1, 32, 0, stream>>>((unsigned long long)limit_ns, status);
+  LLM_CHECK_LAUNCH("wait_probe");
+  return LLM_OK;
+}

@@ -201,7 +201,7 @@ static int launch_gemv(const void *x, long long ldx, const void *W, void *out, l
   int k_split = 1;
   while (k_split < GEMV_WARPS && n_kblocks / (k_split * 2) >= 4 * UNROLL) k_split *= 2;
   while (k_split < GEMV_WARPS && n_kblocks / (k_split * 2) >= UNROLL &&
-         (n_out + (GEMV_WARPS / k_split) * 16 * MT - 1) / ((GEMV_WARPS / k_split) * 16 * MT) < 2 * 148)
+         (n_out + (GEMV_WARPS / k_split) * 16 * MT - 1) / ((GEMV_WARPS / k_split) * 16 * MT) < 2 * sm_count())
     k_split *= 2;
   const int row_groups = GEMV_WARPS / k_split;
   const int rows_per_cta = row_groups * 16 * MT;
@@ -231,7 +231,7 @@ LLM_EXPORT int llm_gemv_suggest_parts(int M, int N, int K) {
   const int ctas = (N + 15) / 16;
   const int kblocks = (K + 31) / 32;
   int parts = 1;
-  while (parts < 8 && ctas * parts < 2 * 148 && kblocks / (parts * 2) >= GEMV_WARPS * unroll) parts *= 2;
+  while (parts < 8 && ctas * parts < 2 * sm_count() && kblocks / (parts * 2) >= GEMV_WARPS * unroll) parts *= 2;
   return parts;
 }
 

@@ -115,7 +115,10 @@ LLM_EXPORT int llm_rope_cache_write(int in_dtype, int dtype, const void *qkv, lo
                                     int write_cache, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0, "rope: bad sizes");
-  LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim > 0, "rope: rotated width %d does not fit head size %d", rot_dim, d);
+  // rot_dim 0: nothing is rotated (a mixer without a position encoding); queries pass through and
+  // keys and values are appended as they are
+  LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim >= 0 && (rot_dim == 0 || table != nullptr),
+              "rope: rotated width %d does not fit head size %d", rot_dim, d);
   LLM_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope: too many heads for one launch");
   const int n_slots = write_cache ? n_heads + 2 * n_kv : n_heads;
   const bool vec = d % 8 == 0 && rot_dim == d && row_stride % 4 == 0 && q_stride % 4 == 0 &&

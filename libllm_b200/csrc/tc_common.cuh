@@ -46,20 +46,24 @@ __device__ __forceinline__ bool mbar_try_sleep(unsigned bar, unsigned parity, un
 }
 // Waits for the barrier's phase with a time limit.  Returns false when the limit ran out or
 // another warp has given up (`*abort_flag` set); the first to give up records `code`.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, int *status,
-                                          int code) {
+__device__ __forceinline__ bool mbar_wait_limit(unsigned bar, unsigned parity, volatile int *abort_flag, int *status,
+                                                int code, unsigned long long limit_ns) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = globaltimer();
   for (;;) {
     for (int i = 0; i < 8; ++i)
       if (mbar_try_sleep(bar, parity, 20000u)) return true;
     if (*abort_flag) return mbar_try(bar, parity);
-    if (globaltimer() - t0 > TC_WAIT_NS) {
+    if (globaltimer() - t0 > limit_ns) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, code);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, int *status,
+                                          int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, code, TC_WAIT_NS);
 }
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y, unsigned bar) {
   asm volatile(
@@ -235,17 +239,6 @@ int get_map(const void *ptr, long long rows, long long cols, long long ld, int b
   cache.emplace(key, m);
   *out = m;
   return LLM_OK;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
 }
 
 }  // namespace

@@ -41,3 +41,8 @@ class UnsupportedError(LlmError):
 
 class ExtensionError(LlmError):
     """The CUDA extension is missing, cannot be built or reported a launch failure."""
+
+
+class EndOfSequence(LlmError):
+    """A completion has ended (the reference's LLM_ERROR_EOF)."""
+    code = 0x0103  # LLM_ERROR_EOF

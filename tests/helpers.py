@@ -39,7 +39,7 @@ def model_folder(name: str, seed: int = 1, config: dict = None) -> str:
     global _tmp
     key = (name, seed)
     if key not in _folders:
-        from libllm_b200.weights.random_model import create_random_model
+        from libllm_b200.weights import create_random_model
         if _tmp is None:
             _tmp = tempfile.TemporaryDirectory(prefix="libllm_b200_tests_")
         d = os.path.join(_tmp.name, f"{name}_{seed}")
@@ -73,6 +73,34 @@ def plain_weights(folder: str) -> Dict[str, torch.Tensor]:
             raise ValueError(e["dtype"])
         out[name] = t.reshape(e["shape"]).to(torch.float64)
     return out
+
+
+def write_safetensors(path: str, tensors) -> None:
+    """A safetensors file from a dict of torch tensors, written without the library."""
+    import json
+    import struct
+    codes = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16", torch.float64: "F64", torch.int64: "I64",
+             torch.int32: "I32", torch.uint8: "U8"}
+    header, blobs, off = {}, [], 0
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        raw = (t.view(torch.int16) if t.dtype == torch.bfloat16 else t).numpy().tobytes()
+        header[name] = dict(dtype=codes[t.dtype], shape=list(t.shape), data_offsets=[off, off + len(raw)])
+        off += len(raw)
+        blobs.append(raw)
+    text = json.dumps(header).encode()
+    text += b" " * ((8 - len(text) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(text)) + text + b"".join(blobs))
+
+
+def rotary_frequencies(rotary_dim: int, theta: float, scaling):
+    """The library's own frequencies (parts/builtin.cc), for tests that build a kernel's table."""
+    import ctypes
+    from libllm_b200 import _lib
+    out = (ctypes.c_double * (rotary_dim // 2))()
+    _lib.check(_lib.lib().llm_rotary_frequencies(rotary_dim, float(theta), _lib.Json(scaling).ref if scaling else _lib.Json(None).ref, out))
+    return list(out)
 
 
 def tokens_for(name: str, length: int, seed: int) -> List[int]:

@@ -24,7 +24,7 @@ def replay_batch(engine: Engine, requests: Sequence[Tuple[str, List[int], int]])
             piece = toks[fed[rid]:fed[rid] + n]
             items.append(StepItem(slots[rid], piece, list(range(len(piece)))))
             ids.append((rid, len(piece)))
-        logits = engine.step(items).float().cpu()
+        logits = torch.from_numpy(engine.step(items))
         o = 0
         for rid, n in ids:
             rows[rid].append(logits[o:o + n])
@@ -38,5 +38,5 @@ def replay_batch(engine: Engine, requests: Sequence[Tuple[str, List[int], int]])
                 nxt.append(r)
         live = nxt
         first = False
-    engine.cache.check()
+    engine.cache_check()
     return {rid: torch.cat(v, 0) for rid, v in rows.items()}

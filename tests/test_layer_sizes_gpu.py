@@ -74,10 +74,9 @@ def check_against_the_floor(got, name, folder, toks, what):
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
 @pytest.mark.parametrize("name", sorted(SIZES))
 def test_layer_sizes_of_the_benchmark_models(name, dtype):
-    from libllm_b200.engine import Engine, Model
+    from libllm_b200.engine import Engine
     folder = model_folder("size_" + name, seed=9, config=SIZES[name])
-    model = Model.from_folder(folder, dtype=dtype, device="cuda:0", max_positions=256)
-    engine = Engine(model, max_tokens=512)
+    engine = Engine.from_folder(folder, dtype=dtype, max_tokens=512, max_seq_len=256)
     g = torch.Generator().manual_seed(3)
     long_ = torch.randint(0, 1000, (70,), generator=g).tolist()
     short = torch.randint(0, 1000, (9,), generator=g).tolist()
@@ -87,8 +86,7 @@ def test_layer_sizes_of_the_benchmark_models(name, dtype):
             check_float32(got[rid], name, folder, toks, f"{name} {rid}")
         else:
             check_against_the_floor(got[rid], name, folder, toks, f"{name} {rid}")
-    del engine, model
-    torch.cuda.empty_cache()
+    engine.close()
 
 
 @pytest.mark.parametrize("name,n_prompt", [("3b", 300), ("8b", 257)])
@@ -96,15 +94,13 @@ def test_a_long_prompt_at_head_size_128(name, n_prompt):
     """Prompts of more than 128 tokens at head size 128 take the prompt attention's form with 256
     query rows a CTA: here through the engine (the kernel tests call both forms directly), with a
     prompt that ends inside a query tile and inside a key tile, beside a short one."""
-    from libllm_b200.engine import Engine, Model
+    from libllm_b200.engine import Engine
     folder = model_folder("size_" + name, seed=9, config=SIZES[name])
-    model = Model.from_folder(folder, dtype="bfloat16", device="cuda:0", max_positions=512)
-    engine = Engine(model, max_tokens=1024)
+    engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024, max_seq_len=512)
     g = torch.Generator().manual_seed(4)
     long_ = torch.randint(0, 1000, (n_prompt + 3,), generator=g).tolist()
     short = torch.randint(0, 1000, (140,), generator=g).tolist()
     got = replay_batch(engine, [("long", long_, n_prompt), ("short", short, 137)])
     for rid, toks in (("long", long_), ("short", short)):
         check_against_the_floor(got[rid], name, folder, toks, f"{name} {rid}")
-    del engine, model
-    torch.cuda.empty_cache()
+    engine.close()
