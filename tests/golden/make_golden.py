@@ -202,8 +202,9 @@ def main() -> int:
         assert data.size == (T + 1) * V, (data.size, T, V)
         whole, last_by_token = data[:T * V].reshape(T, V), data[T * V:]
         rows = case["rows"]
-        np.savez(os.path.join(HERE, f"{name}.npz"), rows=np.array(rows), logits=whole[rows].astype(np.float32),
-                 last_token_by_token=last_by_token.astype(np.float32), checksum=np.array(cases.checksum(w)))
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), rows=np.array(rows), logits=whole[rows].astype(np.float32),
+                            last_token_by_token=last_by_token.astype(np.float32), checksum=np.array(cases.checksum(w)),
+                            **{"w/" + k: t.numpy().astype(np.float16) for k, t in w.items()})
         print(f"{name}: {T} tokens, rows {rows}, max |whole[-1] - token by token| = "
               f"{np.abs(whole[-1] - last_by_token).max():.3e}")
     return 0

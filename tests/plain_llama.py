@@ -207,8 +207,9 @@ def decoder_layer(x, positions, w, i: int, c: dict, act_dtype=None) -> torch.Ten
                             p + "mlp.", act_dtype)
 
 
-def forward_logits(c: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], act_dtype=None) -> torch.Tensor:
-    """Logits at every position of one whole sequence, [T, vocab], float64: embedding,
+def forward_logits(c: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], act_dtype=None,
+                   rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits at every position (or at ``rows``) of one whole sequence, [T, vocab], float64: embedding,
     the layers in order, the last norm (src/libllm/llama.cc:294-303), then the output
     matrix (src/libllm/llama.cc:305-308), which is the embedding table when
     ``tie_word_embeddings`` is set (the exporter writes the checkpoint's lm_head, which
@@ -217,6 +218,8 @@ def forward_logits(c: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], act_
     positions = torch.arange(len(ids))
     for i in range(c["num_hidden_layers"]):
         x = decoder_layer(x, positions, w, i, c, act_dtype)
+    if rows is not None:
+        x = x[list(rows)]
     x = stored(rms_norm(x, w["model.norm.weight"], c["rms_norm_eps"]), act_dtype)
     head = w["model.embed_tokens.weight"] if c["tie_word_embeddings"] else w["lm_head.weight"]
     return linear(x, head)

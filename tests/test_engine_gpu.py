@@ -172,3 +172,28 @@ def test_wanted_places_in_any_order_across_pieces():
     engine.close_sequence(sb)
     check_logits(got[:3], plain(c, w, a)[[99, 3, 50]], "float32", "rows of a")
     check_logits(got[3:], plain(c, w, b)[[29, 0]], "float32", "rows of b")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_tensors_stored_in_other_types_load_to_the_same_model(dtype):
+    """Weights handed over in host memory as bfloat16, float32 or float64 (the same values) are
+    converted by role: operands of products to the engine's type, norm weights to 32-bit."""
+    from libllm_b200.engine import Engine, StepItem
+    folder = model_folder("A")
+    w = plain_weights(folder)                                  # float64, the stored bfloat16 values
+    toks = tokens_for("A", 40, 31)
+    outs = []
+    for conv in (lambda t: t.to(torch.bfloat16), lambda t: t.float(), lambda t: t.double().numpy(), lambda t: t.float().numpy()):
+        engine = Engine.from_tensors(P.read_config(folder) | {"model_type": "llama"}, {k: conv(v) for k, v in w.items()},
+                                     dtype=dtype, max_tokens=128)
+        s = engine.open_sequence()
+        outs.append(torch.from_numpy(engine.step([StepItem(s, toks, [0, 20, 39])])))
+        engine.close()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    check_logits(outs[0], plain(P.read_config(folder), w, toks)[[0, 20, 39]], dtype, "from tensors in host memory")
+    # the folder's own loader gives the same
+    engine, _, _ = setup("A", dtype)
+    s = engine.open_sequence()
+    assert torch.equal(torch.from_numpy(engine.step([StepItem(s, toks, [0, 20, 39])])), outs[0])
+    engine.close_sequence(s)

@@ -24,9 +24,10 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 def test_plain_implementation_matches_the_reference_cpu_code(name):
     case = cases.CASES[name]
     gold = np.load(os.path.join(GOLDEN, f"{name}.npz"))
-    w = cases.weights(case["config"], case["seed"])
-    if cases.checksum(w) != str(gold["checksum"]):
-        pytest.skip("this numpy draws other weights than the one the golden files were made with")
+    # the weights the reference ran with lie in the file (float16, its tensor file's precision), so
+    # the comparison does not hinge on this numpy drawing the same numbers again
+    w = {k[2:]: torch.from_numpy(gold[k].astype(np.float32)) for k in gold.files if k.startswith("w/")}
+    assert cases.checksum(w) == str(gold["checksum"])
     c = dict(case["config"])
     c["rope_table"] = cases.rope_table(c)
     logits = P.forward_logits(c, w, case["ids"])
