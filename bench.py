@@ -84,8 +84,11 @@ class ClockSampler:
         mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=reasons, samples=len(sm))
+        # "under load": a run also spends time where the GPU idles at a few hundred MHz (a model file
+        # being written, a process starting); those samples say nothing about the timed kernels
+        busy = [x for x in sm if x >= 0.5 * max(sm)] if sm else []
+        return dict(sm_mhz=statistics.median(busy) if busy else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm), samples_under_load=len(busy))
 
 
 def model_numbers(c):
@@ -246,11 +249,63 @@ def run_workload(args):
 
 
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "ling0322/libllm's root is not pip-installable; its python/ folder installs only a ctypes "
-                      "wrapper (pylibllm) whose libllm.so is not built offline (CMake needs downloaded libunwind and "
-                      "FlashAttention sources) and whose symbols no longer exist in llm.h; models must be .llmpkg "
-                      "files exported from downloaded checkpoints"}))
+    """The reference arm: ling0322/libllm's unmodified C++/CUDA code (compiled into baseline/_ref by
+    baseline/reference_arm.py; it has no installable Python package of its engine) at the same layer
+    sizes, batch and prompt length, in its own compute type (float16), timed with a device
+    synchronisation on both sides.  Where it cannot be built or run, one line says why."""
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:600]}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("ling0322/libllm runs on one GPU (every CUDA call of it targets device 0)")
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_arm
+        reference_arm.build()
+    except Exception as e:                       # no checkout, no compiler, a compile error
+        return unavailable(f"the reference could not be compiled here: {e}")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+    except ImportError:
+        pass
+    cfg = dict(LLAMA_1B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    warmup = max(args.warmup, 3)
+    sampler = ClockSampler()
+    sampler.start()
+    try:
+        r = reference_arm.run(cfg, PROMPT, args.batch, args.steps, warmup, CONTEXT)
+    except Exception as e:
+        sampler.stop()
+        return unavailable(f"the reference's driver failed: {e}")
+    clocks = sampler.stop()
+    pk = peaks()
+    wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+    ms, e2e_ms = r["decode_ms_per_step"], r["e2e_ms_per_step"]
+    step_bytes = wbytes + args.batch * (PROMPT + warmup + args.steps // 2) * kv_per_tok
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode tok/s (Llama-3.2-1B layer sizes, batch 8, 2048-token prompts, 4096 context)",
+        "value": round(args.batch * 1000.0 / ms, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "llama-3.2-1b-sizes", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single-gpu",
+                   "weights": "random fp16 N(0,0.02), tied", "attention": "the reference's portable path (FlashAttention off)",
+                   "l2": "step reads more than L2 (no flush)", "peaks": pk["source"]},
+        "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 8 * args.batch,
+                "d2h_bytes_per_step": 8 * args.batch},
+        "clocks": clocks,
+        "prefill": {"value": round(PROMPT * 1000.0 / r["prefill_ms"], 1), "tokens": PROMPT, "ms": round(r["prefill_ms"], 4),
+                    "frac": round(flops_fn(PROMPT) / (r["prefill_ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)}}))
     return 0
 
 
