@@ -468,7 +468,9 @@ def test_tensor_core_product_rows_do_not_depend_on_the_batch():
 
 @pytest.mark.parametrize("n_heads,n_kv,d,window", [(4, 2, 16, None), (3, 1, 32, None), (32, 8, 64, None), (8, 1, 128, None),
                                                      (8, 8, 64, None), (6, 2, 128, 100), (10, 2, 48, None)])
-@pytest.mark.parametrize("chunk,n_splits", [(64, 16), (192, 6), (1024, 1), (0, 5)])     # 0: each length cut into 5 runs
+# up to 16 splits are joined through a cluster's shared memory, more through scratch in global memory;
+# chunk 0: each length cut into 5 runs
+@pytest.mark.parametrize("chunk,n_splits", [(64, 16), (64, 18), (192, 6), (1024, 1), (0, 5)])
 def test_attention_decode_fused(n_heads, n_kv, d, window, chunk, n_splits):
     """Rotation, cache append, attention and the joining of splits in one launch: the outputs
     against the plain rotation + attention, the cache rows it must have written, and a second
