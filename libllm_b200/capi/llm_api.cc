@@ -305,6 +305,7 @@ LLM_API int32_t llm_model_get_info(llm_model_t *m, llm_json_t *info) {
     j.set("steps_run", (int64_t)e.steps_run());
     j.set("graphs_captured", (int64_t)e.graphs_captured());
     j.set("graph_replays", (int64_t)e.graph_replays());
+    j.set("chain_launches", (int64_t)e.chain_launches());
     j.set("last_tokens_capacity", e.last_tokens_capacity());
     j.set("last_step_h2d_bytes", (int64_t)e.last_step_h2d_bytes());
     j.set("last_step_d2h_bytes", (int64_t)e.last_step_d2h_bytes());

@@ -54,6 +54,7 @@ FAMILIES: Dict[str, dict] = {
     "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh", "attention_decode.h"]),
     "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "gemm_tc": dict(sources=["gemm_tc.cu"], headers=["common.cuh", "tc_common.cuh"]),
+    "gemm_chain": dict(sources=["gemm_chain.cu"], headers=["common.cuh", "tc_common.cuh"]),
     "attention_prefill_tc": dict(sources=["attention_prefill_tc.cu"], headers=["common.cuh", "tc_common.cuh"]),
     "attention_decode_tc": dict(sources=["attention_decode_tc.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
 }

@@ -200,6 +200,29 @@ void gemm_tc(const Act &x, const Weight &w, const Act &out, bool swiglu, int *st
 }
 LLM_KERNEL("gemm_tc", llm_gemm_tc_wait_probe, long long, int *, cudaStream_t)
 void gemm_tc_wait_probe(long long limit_ns, int *status, cudaStream_t s) { LLM_CALL("gemm_tc", llm_gemm_tc_wait_probe, limit_ns, status, s); }
+LLM_KERNEL("gemm_chain", llm_gemm_chain, const ChainJob *, int, int *, int *, cudaStream_t)
+static int chain_limit(const char *name) {
+  return resolve<int (*)()>("gemm_chain", name)();
+}
+int gemm_chain_max_jobs() {
+  static const int v = chain_limit("llm_gemm_chain_max_jobs");
+  return v;
+}
+int gemm_chain_max_tokens() {
+  static const int v = chain_limit("llm_gemm_chain_max_tokens");
+  return v;
+}
+int gemm_chain_max_hidden() {
+  static const int v = chain_limit("llm_gemm_chain_max_hidden");
+  return v;
+}
+int gemm_chain_counters() {
+  static const int v = chain_limit("llm_gemm_chain_counters");
+  return v;
+}
+void gemm_chain(const ChainJob *jobs, int n_jobs, int *counters, int *status, cudaStream_t s) {
+  LLM_CALL("gemm_chain", llm_gemm_chain, jobs, n_jobs, counters, status, s);
+}
 bool gemv_supported(const Act &x, const Weight &w) {
   return x.dtype == DType::BF16 && w.dtype == DType::BF16 && x.rows > 0 && x.rows <= 64 && x.cols % 8 == 0 && x.ld % 8 == 0 &&
          (uintptr_t)x.data % 16 == 0 && (uintptr_t)w.data() % 16 == 0;

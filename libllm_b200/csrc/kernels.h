@@ -41,6 +41,32 @@ bool gemm_tc_supported(const Act &x, const Weight &w);
 int gemm_tc_suggest_parts(int M, int N, int K);
 void gemm_tc(const Act &x, const Weight &w, const Act &out, bool swiglu, int *status, cudaStream_t s);
 void gemm_tc_wait_probe(long long limit_ns, int *status, cudaStream_t s);
+// One job of a chain of products and norms run as one launch (csrc/gemm_chain.cu, which has the
+// same structure under the name llm_chain_job).
+struct ChainJob {
+  int kind;                 // 0 product, 1 SwiGLU product, 2 add + RMSNorm
+  int dep0, dep1;           // jobs of the chain that must be complete first; -1: none
+  const void *x;
+  long long ldx;
+  const void *w;
+  void *out;
+  long long ldo;
+  int M, N, K, k_parts;
+  long long part_stride;
+  float *resid;
+  const float *delta;
+  int delta_parts;
+  long long delta_stride;
+  const float *weight;
+  float eps;
+  const int *rows;
+  int n_rows, hidden;
+};
+int gemm_chain_max_jobs();
+int gemm_chain_max_tokens();
+int gemm_chain_max_hidden();
+int gemm_chain_counters();
+void gemm_chain(const ChainJob *jobs, int n_jobs, int *counters, int *status, cudaStream_t s);
 bool gemv_supported(const Act &x, const Weight &w);
 int gemv_suggest_parts(int M, int N, int K);
 void gemv_bf16(const Act &x, const Weight &w, const Act &out, bool swiglu, cudaStream_t s);

@@ -383,6 +383,50 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = 
     return out
 
 
+# ------------------------------------------------------------------ a chain of products and norms in one launch
+class ChainJob(ctypes.Structure):
+    """The kernel library's llm_chain_job (libllm_b200/csrc/gemm_chain.cu)."""
+    _fields_ = [("kind", c_int), ("dep0", c_int), ("dep1", c_int), ("x", c_void_p), ("ldx", c_longlong),
+                ("w", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("M", c_int), ("N", c_int), ("K", c_int),
+                ("k_parts", c_int), ("part_stride", c_longlong), ("resid", c_void_p), ("delta", c_void_p),
+                ("delta_parts", c_int), ("delta_stride", c_longlong), ("weight", c_void_p), ("eps", ctypes.c_float),
+                ("rows", c_void_p), ("n_rows", c_int), ("hidden", c_int)]
+
+
+def chain_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False, deps=(-1, -1)) -> ChainJob:
+    """A product job: out [M, N] or [parts, M, N] 32-bit, or with ``swiglu`` [M, N/2] bfloat16."""
+    _on_gpu(x, w, out)
+    M, K = x.shape
+    j = ChainJob()
+    j.kind, j.dep0, j.dep1 = (1 if swiglu else 0), deps[0], deps[1]
+    j.x, j.ldx, j.w, j.out = _ptr(x), (x.stride(0) if M > 1 else K), _ptr(w), _ptr(out)
+    j.ldo = out.stride(-2) if M > 1 else out.shape[-1]
+    j.M, j.N, j.K = M, w.shape[0], K
+    j.k_parts, j.part_stride = (out.shape[0], out.stride(0)) if out.dim() == 3 else (1, 0)
+    return j
+
+
+def chain_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+               rows: Optional[torch.Tensor] = None, deps=(-1, -1)) -> ChainJob:
+    """An add + RMSNorm job: delta [parts, T, H] or [T, H] 32-bit is added to resid [T, H] first."""
+    j = ChainJob()
+    j.kind, j.dep0, j.dep1 = 2, deps[0], deps[1]
+    j.resid, j.weight, j.out, j.eps = _ptr(resid), _ptr(weight), _ptr(out), eps
+    if delta is not None:
+        j.delta = _ptr(delta)
+        j.delta_parts, j.delta_stride = (delta.shape[0], delta.stride(0)) if delta.dim() == 3 else (1, 0)
+    j.rows = _ptr(rows)
+    j.n_rows, j.hidden = out.shape[0], resid.shape[1]
+    return j
+
+
+def gemm_chain(jobs, counters: torch.Tensor) -> None:
+    """Runs the jobs in order as one launch; ``counters`` are at least 9 int32 zeros, left zero."""
+    arr = (ChainJob * len(jobs))(*jobs)
+    _call("gemm_chain", "llm_gemm_chain", [c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+          ctypes.cast(arr, c_void_p), len(jobs), _ptr(counters), _ptr(tc_status(counters.device)), _stream())
+
+
 # ------------------------------------------------------------------ decode attention on tensor cores, rotation fused
 def attention_decode_tc_supported(head_dim: int, page_size: int, group: int) -> bool:
     lib = build.load("attention_decode_tc")

@@ -10,6 +10,7 @@
 
 #include "config/config.h"
 #include "csrc/kernels.h"
+#include "parts/chain.h"
 #include "parts/linear.h"
 #include "sampling/rng.h"
 #include "util/log.h"
@@ -171,9 +172,13 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
     StateView sv = cache.state_view((int)i);
     layers_[(size_t)e.layer]->forward(ctx, stream, has_cache ? &lc : nullptr, sv.empty() ? nullptr : &sv);
   }
-  if (ctx.n_want == 0) return Act();
+  if (ctx.n_want == 0) {
+    flush_chain(ctx);
+    return Act();
+  }
   Act h = final_norm_->forward(ctx, stream, ctx.want_rows, ctx.n_want);
   Act logits = linear(ctx, h, *head_, nullptr, DType::F32);
+  flush_chain(ctx);
   if (spec_.logit_scale != 1.0 || spec_.logit_softcap > 0.0)
     kernels::logit_transform((float *)logits.data, logits.rows * logits.cols, (float)spec_.logit_scale, (float)spec_.logit_softcap,
                              ctx.stream);

@@ -6,6 +6,8 @@
 #include <set>
 
 #include "csrc/kernels.h"
+#include "parts/chain.h"
+#include "parts/linear.h"
 
 namespace llm {
 
@@ -128,7 +130,7 @@ Engine::Engine(std::unique_ptr<Model> model, const Options &options) : model_(st
   cache_.reset(new KVCache(needs, has, model_->state_needs(), opt_.max_tokens, model_->dtype(), opt_.page_size, opt_.max_slots));
   LLM_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
   status_.allocate(sizeof(int), true);
-  counters_.allocate(sizeof(int) << 18, true);
+  counters_.allocate((sizeof(int) << 18) + 64 * sizeof(int), true);      // the last 64 are the chained kernel's
   // The tokens the last sampling step drew, kept on the device: the next step can take them from
   // here (StepItem::fed_row) while the host is still reading them back.
   last_capacity_ = std::max(opt_.max_step_tokens, 1024);
@@ -163,9 +165,13 @@ void Engine::synchronize() {
   LLM_CUDA(cudaStreamSynchronize(stream_));
 }
 
+long long Engine::chain_launches() const { return chain_launches_ + (chain_ ? chain_->launches() : 0); }
+
 void Engine::raise_status(int code) {
   cudaMemsetAsync(status_.get(), 0, sizeof(int), stream_);
-  LLM_THROW(Extension, "a tensor-core kernel gave up waiting on a barrier (code %d: 1 loader, 2-3 issue, 4-6 epilogue, 9 a probe); "
+  cudaMemsetAsync(counters_.get(), 0, counters_.bytes(), stream_);      // a kernel that gave up may have left its counts
+  LLM_THROW(Extension, "a tensor-core kernel gave up waiting on a barrier (code %d: 1 loader, 2-3 issue, 4-6 epilogue, 7-8 a job of a "
+                       "chain, 9 a probe); "
                        "the step's results are not valid", code);
 }
 
@@ -267,6 +273,14 @@ StepContext Engine::context(Descriptor &d, const std::vector<Piece> &pieces, int
   ctx.zero_counters = counters_.as<int>();
   ctx.n_zero_counters = 1 << 18;
   ctx.sm_count = sm_count_;
+  // Steps of single tokens in bfloat16 queue their products and norms and launch them together.
+  ctx.chain = nullptr;
+  if (decode_only && ctx.dtype == DType::BF16 && fast_switches().gemm_tc && fast_switches().gemm_chain &&
+      kernels::available("gemm_chain") && d.n_tokens <= kernels::gemm_chain_max_tokens()) {
+    if (chain_) chain_launches_ += chain_->launches();
+    chain_.reset(new Chain(counters_.as<int>() + (1 << 18), status_.as<int>()));
+    ctx.chain = chain_.get();
+  }
   tables->clear();
   for (size_t g = 0; g < d.widths.size(); ++g) tables->push_back(d.dev(Descriptor::Tables + (int)g));
   return ctx;

@@ -124,6 +124,7 @@ class Engine {
   long long steps_run() const { return steps_run_; }
   long long graphs_captured() const { return graphs_captured_; }
   long long graph_replays() const { return graph_replays_; }
+  long long chain_launches() const;   // launches of queued products and norms (outside graph replays)
   int last_tokens_capacity() const { return last_capacity_; }
   // Bytes the last step brought from pinned host memory to the device (its descriptor) and from
   // the device to the host by itself (a single-token step's sampled tokens and status word).
@@ -163,6 +164,7 @@ class Engine {
   int sm_count_ = 148;
   Arena scratch_, results_;
   DeviceBuffer status_, counters_, last_tokens_;
+  std::unique_ptr<Chain> chain_;     // the queue of the step being launched (parts/chain.h)
   int last_capacity_ = 0;
   std::vector<std::unique_ptr<Descriptor>> eager_desc_;
   size_t eager_turn_ = 0;
@@ -176,6 +178,7 @@ class Engine {
   std::map<GraphKey, std::unique_ptr<DecodeGraph>> graphs_[2];
   std::map<GraphKey, int> graph_turn_;
   DecodeGraph *last_graph_ = nullptr;
+  long long chain_launches_ = 0;
   long long steps_run_ = 0, graphs_captured_ = 0, graph_replays_ = 0, last_h2d_ = 0, last_d2h_ = 0;
 };
 

@@ -4,6 +4,7 @@
 
 #include "config/config.h"
 #include "csrc/kernels.h"
+#include "parts/chain.h"
 #include "parts/linear.h"
 #include "parts/part.h"
 #include "util/log.h"
@@ -32,6 +33,13 @@ class RMSNorm : public Norm {
   Act forward(StepContext &ctx, ResidualStream &stream, const int *rows, int n_rows) override {
     const int64_t n = rows ? n_rows : stream.rows;
     Act out = ctx.arena->act(ctx.dtype, n, size_);
+    if (ctx.chain && ctx.dtype == DType::BF16 &&
+        ctx.chain->add_norm(stream.resid, stream.pending.data ? &stream.pending : nullptr, weight_.buf.as<float>(), (float)eps_,
+                            out.data, rows, (int)n, (int)size_, ctx.stream)) {
+      if (!rows) stream.pending = Act();
+      return out;
+    }
+    flush_chain(ctx);
     kernels::add_rmsnorm(stream.resid, stream.pending.data ? &stream.pending : nullptr, weight_.buf.as<float>(), (float)eps_,
                          out.data, ctx.dtype, rows, (int)n, (int)size_, ctx.stream);
     if (!rows) stream.pending = Act();
@@ -255,6 +263,7 @@ class Attention : public Mixer {
     const bool fused = table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
                        kernels::available("attention_decode_tc") && kernels::attention_decode_tc_supported(d_, cache->page_size, group);
     Act qkv = linear(ctx, x, w_qkv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, DType::F32, fused);
+    flush_chain(ctx);
     if (fused) {
       const int max_len = std::max(ctx.max_kv_len, 1);
       const int pairs = std::max(1, ctx.n_seqs * n_kv_);
@@ -383,11 +392,13 @@ class SwiGLU : public FeedForward {
       if (!m.data && f.gemm_tc && x.rows >= f.fused_gate_up_tokens && x.cols <= f.fused_gate_up_max_k &&
           kernels::gemm_tc_supported(x, w_gate_up_)) {
         m = ctx.arena->act(ctx.dtype, x.rows, inter_);
+        flush_chain(ctx);
         kernels::gemm_tc(x, w_gate_up_, m, true, ctx.tc_status, ctx.stream);
       }
     }
     if (!m.data) {
       Act gu = linear(ctx, x, w_gate_up_, nullptr, DType::F32);
+      flush_chain(ctx);
       m = ctx.arena->act(ctx.dtype, x.rows, inter_);
       kernels::swiglu(gu, m.data, ctx.dtype, ctx.stream);
     }

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "csrc/kernels.h"
+#include "parts/chain.h"
 #include "util/log.h"
 
 namespace llm {
@@ -27,6 +28,7 @@ const FastSwitches &fast_switches() {
     f.prefill_attention_tc = !off("LIBLLM_B200_NO_PREFILL_ATTENTION_TC");
     f.decode_attention_tc = !off("LIBLLM_B200_NO_DECODE_ATTENTION_TC");
     f.library_gemm = !off("LIBLLM_B200_NO_LIBRARY_GEMM");
+    f.gemm_chain = off("LIBLLM_B200_GEMM_CHAIN");      // set: on (measured no faster than the launches it replaces)
     f.tc_tokens = num("LIBLLM_B200_TC_TOKENS", 256);
     f.fused_gate_up_tokens = num("LIBLLM_B200_FUSED_GATE_UP_TOKENS", 1024);
     f.gemv_tokens = num("LIBLLM_B200_GEMV_TOKENS", 0);
@@ -40,6 +42,7 @@ std::vector<std::string> product_families(DType dtype) {
   if (dtype == DType::BF16) {
     const FastSwitches &f = fast_switches();
     if (f.gemm_tc) fams.push_back("gemm_tc");
+    if (f.gemm_tc && f.gemm_chain) fams.push_back("gemm_chain");
     if (f.gemv && f.gemv_tokens > 0) fams.push_back("gemv");
   }
   return fams;
@@ -134,9 +137,12 @@ Act small_batch_linear(StepContext &ctx, const Act &x, const Weight &w, DType ou
     int parts = 1;
     if (parts_ok && !swiglu && out_dtype == DType::F32) parts = kernels::gemm_tc_suggest_parts(T, n, K);
     Act out = ctx.arena->act(out_dtype, T, n, parts > 1 ? parts : 1);
+    if (ctx.chain && ctx.chain->add_product(x, w, out, swiglu, ctx.stream)) return out;
+    flush_chain(ctx);
     kernels::gemm_tc(x, w, out, swiglu, ctx.tc_status, ctx.stream);
     return out;
   }
+  flush_chain(ctx);
   if (!use_gemv) return none;
   int parts = 1;
   if (parts_ok && !swiglu && out_dtype == DType::F32) parts = kernels::gemv_suggest_parts(T, n, K);
@@ -150,6 +156,7 @@ Act linear(StepContext &ctx, const Act &x, const Weight &w, const float *bias, D
     LLM_THROW(InvalidArg, "linear: activations of width %lld meet a matrix of width %lld", (long long)x.cols, (long long)w.cols);
   const int T = (int)x.rows;
   if (x.dtype == DType::F32 || bias != nullptr) {
+    flush_chain(ctx);
     // the true 32-bit path; and, in bfloat16, a product with a bias (CUDA cores: such a model pays
     // for it, which load() says once)
     Act out = ctx.arena->act(out_dtype, T, w.rows);

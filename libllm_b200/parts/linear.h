@@ -14,6 +14,7 @@ namespace llm {
 struct FastSwitches {
   bool gemm_tc = true, gemv = true, decode_attention = true, prefill_attention = true, prefill_attention_tc = true,
        decode_attention_tc = true, library_gemm = true;
+  bool gemm_chain = false;             // queue a decoding step's products and norms into single launches (parts/chain.h)
   int tc_tokens = 256;                 // steps of up to this many tokens take the tcgen05 product
   int fused_gate_up_tokens = 1024;     // prompt steps from this many tokens fuse SwiGLU into the product ...
   int fused_gate_up_max_k = 3072;      // ... when the width is at most this

@@ -32,6 +32,7 @@
 namespace llm {
 
 class Arena;
+class Chain;
 
 // What a part may know about the engine it is built for.
 struct BuildEnv {
@@ -112,6 +113,9 @@ struct StepContext {
   int *zero_counters = nullptr;      // int32 zeros that kernels may count in if they leave them zero
   int n_zero_counters = 0;
   int sm_count = 148;                // streaming multiprocessors of the device
+  // When set, products and norms are queued and launched together (parts/chain.h).  Whoever
+  // launches anything else on `stream`, or hands a buffer to code outside, calls flush_chain() first.
+  Chain *chain = nullptr;
 };
 
 // Device memory for a step's activations: handed out front to back, taken back all at once.

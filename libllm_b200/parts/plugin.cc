@@ -5,6 +5,7 @@
 #include "config/config.h"
 #include "csrc/kernels.h"
 #include "include/llm_plugin.h"
+#include "parts/chain.h"
 #include "parts/part.h"
 
 namespace llm {
@@ -156,6 +157,7 @@ class PluginMixer : public Mixer {
   CacheNeed cache_need() const override { return cache_; }
   std::vector<StateNeed> state_need() const override { return state_; }
   Act forward(StepContext &ctx, const Act &x, LayerCache *cache, StateView *state) override {
+    flush_chain(ctx);                  // the part launches on the stream itself
     const int64_t width = core_.vt().out_width > 0 ? core_.vt().out_width : x.cols;
     Act out = ctx.arena->act(DType::F32, x.rows, width);
     const llm_step_t step = to_c(ctx);
@@ -212,6 +214,7 @@ class PluginFeedForward : public FeedForward {
   void load(const Loader &l) override { core_.load(l); }
   bool capturable() const override { return core_.vt().capturable != 0; }
   Act forward(StepContext &ctx, const Act &x) override {
+    flush_chain(ctx);
     const int64_t width = core_.vt().out_width > 0 ? core_.vt().out_width : x.cols;
     Act out = ctx.arena->act(DType::F32, x.rows, width);
     const llm_step_t step = to_c(ctx);
@@ -247,6 +250,7 @@ class PluginPosition : public PositionEncoding {
   void rotate_and_store(StepContext &ctx, const Act &qkv, const Act &q_out, const QkvLayout &l, LayerCache &cache) override {
     int rows = 0, rot = 0;
     const float *table = half_split_table(&rows, &rot);
+    flush_chain(ctx);
     kernels::rope_cache_write(qkv, q_out, l.n_heads, l.n_kv_heads, l.head_dim, table, rows, rot, ctx.tok_seq, ctx.tok_pos,
                               cache.page_table, cache.table_width, cache.k, cache.v, cache.page_size, cache.writes, ctx.stream);
   }

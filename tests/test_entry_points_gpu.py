@@ -246,8 +246,9 @@ def test_a_wait_that_runs_out_is_seen_by_the_next_result():
 
 
 # ------------------------------------------------------------------------- trace replay
-def run_trace(folder, dtype, steps, out_dir, max_tokens):
+def run_trace(folder, dtype, steps, out_dir, max_tokens, extra_env=None):
     env = dict(os.environ)
+    env.update(extra_env or {})
     proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype",
                              dtype, "--out", out_dir, "--max-tokens", str(max_tokens)],
                             stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
@@ -328,6 +329,38 @@ def test_trace_run_whole_last_32_and_unequal_batches(name, dtype, tmp_path):
         for j, n in enumerate(lens):
             toks = tokens_for(name, n + n_dec - j, 910 + 10 * b + j)
             check_logits(got[f"b{b}r{j}"], P.forward_logits(c, w, toks), dtype, f"trace b{b}r{j}")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_trace_run_with_products_and_norms_chained_into_single_launches(name, tmp_path):
+    """The same replay with the decoding steps' products and norms queued into single launches
+    (LIBLLM_B200_GEMM_CHAIN): a request's last tokens one by one, and a batch of unequal lengths."""
+    folder = model_folder(name)
+    c, w = P.read_config(folder), plain_weights(folder)
+    lens = [5, 9, 12] if name == "A" else [1, 7, 33, 70]
+    long_ = tokens_for(name, 100, 900)
+    steps = trace_of([("tail", long_, 68)], 0)
+    reqs = [(f"r{j}", tokens_for(name, n + 12 - j, 930 + j), n) for j, n in enumerate(lens)]
+    steps += trace_of(reqs, len(steps))
+    cap = max(sum((n + 12 + 63) // 64 * 64 for n in lens), 128)
+    out_dir = str(tmp_path / "out")
+    run_trace(folder, "bfloat16", steps, out_dir, cap, {"LIBLLM_B200_GEMM_CHAIN": "1"})
+    got = collect(steps, out_dir, c["vocab_size"])
+    check_logits(got["tail"], P.forward_logits(c, w, long_), "bfloat16", "chained tail")
+    for j, n in enumerate(lens):
+        check_logits(got[f"r{j}"], P.forward_logits(c, w, tokens_for(name, n + 12 - j, 930 + j)), "bfloat16", f"chained r{j}")
+    # and the switch does what it says: such an engine launches chains, one without it none
+    script = ("import sys, json; from libllm_b200 import Model; m = Model(sys.argv[1], dtype='bfloat16', max_tokens=256); "
+              "m.generate([[1, 2, 3]], max_new_tokens=3, temperature=0.0, stop_token_ids=[]); "
+              "print(json.dumps(m.engine.info()['chain_launches']))")
+    for on in (True, False):
+        env = dict(os.environ, PYTHONPATH=ROOT)
+        env.pop("LIBLLM_B200_GEMM_CHAIN", None)
+        if on:
+            env["LIBLLM_B200_GEMM_CHAIN"] = "1"
+        out = subprocess.run([sys.executable, "-c", script, folder], capture_output=True, text=True, env=env, timeout=300)
+        assert out.returncode == 0, out.stderr
+        assert (int(out.stdout.strip().splitlines()[-1]) > 0) == on
 
 
 def test_tokens_fed_on_the_device_give_the_same_steps_as_tokens_from_the_host():

@@ -637,3 +637,87 @@ def test_copy_words_between_pinned_host_memory_and_the_device():
     assert torch.equal(back, host * 3)
     with pytest.raises(ExtensionError):
         ops.copy_words(torch.zeros(4, dtype=torch.int32), dev, 4)
+
+
+# ---------------------------------------------------------------- a chain of products and norms in one launch
+def _chain_case(T, Kq, H, inter, V, parts_o, parts_d, seed, repeats=3):
+    from libllm_b200.csrc import ops
+    eps = 3e-5
+    x0 = rnd((T, Kq), "bfloat16", seed)
+    wo = rnd((H, Kq), "bfloat16", seed + 1, Kq ** -0.5)
+    wgu = rnd((2 * inter, H), "bfloat16", seed + 2, H ** -0.5)
+    wd = rnd((H, inter), "bfloat16", seed + 3, inter ** -0.5)
+    wh = rnd((V, H), "bfloat16", seed + 4, H ** -0.5)
+    n1 = (1 + 0.1 * rnd((H,), "float32", seed + 5))
+    n2 = (1 + 0.1 * rnd((H,), "float32", seed + 6))
+    resid0 = rnd((T, H), "float32", seed + 7)
+    rows = torch.tensor([T - 1, 0, T // 2][:min(3, T)], dtype=torch.int32, device=DEV)
+    W = rows.numel()
+
+    # the plain computation, rounding to bfloat16 where the chain does
+    def norm(v, w):
+        return (v * w * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)).to(torch.bfloat16)
+    o = x0.float() @ wo.float().T
+    v1 = resid0 + o
+    h1 = norm(v1, n1)
+    gu = h1.float() @ wgu.float().T
+    m = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).to(torch.bfloat16)
+    d = m.float() @ wd.float().T
+    v2 = v1 + d
+    h2 = norm(v2[rows.long()], n2)
+    logits_ref = h2.float() @ wh.float().T
+
+    counters = torch.zeros(16, dtype=torch.int32, device=DEV)
+    for _ in range(repeats):
+        resid = resid0.clone()
+        o_parts = torch.full((parts_o, T, H), float("nan"), dtype=torch.float32, device=DEV)
+        h1_out = torch.empty((T, H), dtype=torch.bfloat16, device=DEV)
+        m_out = torch.empty((T, inter), dtype=torch.bfloat16, device=DEV)
+        d_parts = torch.full((parts_d, T, H), float("nan"), dtype=torch.float32, device=DEV)
+        h2_out = torch.empty((W, H), dtype=torch.bfloat16, device=DEV)
+        logits = torch.full((W, V), float("nan"), dtype=torch.float32, device=DEV)
+        jobs = [
+            ops.chain_product(x0, wo, o_parts),
+            ops.chain_norm(resid, o_parts, n1, eps, h1_out, deps=(0, -1)),
+            ops.chain_product(h1_out, wgu, m_out, swiglu=True, deps=(1, -1)),
+            ops.chain_product(m_out, wd, d_parts, deps=(2, -1)),
+            ops.chain_norm(resid, d_parts, n2, eps, h2_out, rows=rows, deps=(3, 1)),
+            ops.chain_product(h2_out, wh, logits, deps=(4, -1)),
+        ]
+        ops.gemm_chain(jobs, counters)
+        torch.cuda.synchronize()
+        ops.check_tc_status()
+        assert int(counters.abs().sum()) == 0, "the chain left its counters non-zero"
+        close(resid, v1, "bfloat16")
+        close(h1_out.float(), h1.float(), "bfloat16")
+        close(m_out.float(), m.float(), "bfloat16")
+        close(h2_out.float(), h2.float(), "bfloat16")
+        close(logits, logits_ref, "bfloat16")
+
+
+@pytest.mark.parametrize("T,Kq,H,inter,V,parts_o,parts_d", [
+    (5, 136, 200, 328, 1000, 2, 3),          # sizes that are no power of two, few tiles
+    (16, 512, 1024, 2816, 20000, 4, 8),      # several tiles per CTA and job
+    (23, 264, 520, 1096, 3001, 1, 2),        # 32-token shape, one part
+    (40, 512, 1024, 1536, 9000, 2, 4),       # 64-token shape
+    (1, 2048, 2048, 8192, 32000, 8, 8),      # the engine's widths at batch 1
+])
+def test_gemm_chain_layer(T, Kq, H, inter, V, parts_o, parts_d):
+    _chain_case(T, Kq, H, inter, V, parts_o, parts_d, seed=11)
+
+
+def test_gemm_chain_refuses():
+    from libllm_b200.csrc import ops
+    from libllm_b200.errors import UnsupportedError
+    counters = torch.zeros(16, dtype=torch.int32, device=DEV)
+    x = rnd((65, 64), "bfloat16", 1)
+    w = rnd((128, 64), "bfloat16", 2)
+    out = torch.empty((65, 128), dtype=torch.float32, device=DEV)
+    with pytest.raises(UnsupportedError):
+        ops.gemm_chain([ops.chain_product(x, w, out)], counters)          # more tokens than a chain takes
+    x = rnd((4, 64), "bfloat16", 1)
+    out = torch.empty((4, 128), dtype=torch.float32, device=DEV)
+    with pytest.raises(UnsupportedError):
+        ops.gemm_chain([ops.chain_product(x, w, out, deps=(0, -1))], counters)   # depends on itself
+    with pytest.raises(UnsupportedError):
+        ops.gemm_chain([ops.chain_product(x, w, out)] * 9, counters)      # more jobs than one launch holds
