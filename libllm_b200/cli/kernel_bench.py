@@ -77,10 +77,8 @@ def report(name, us, bytes_moved=None, flops=None, **sizes):
 # ---------------------------------------------------------------------------------- kernels
 def bench_gemv(args, timer, M=None, N=None, K=None, swiglu=None, name="gemv"):
     import torch
-    from ..parts import fast
+    from ..csrc import ops
     M, N, K = M or args.m, N or args.n, K or args.k
-    fast.GEMV_TOKENS = 64                       # time the weight streamer at any size it takes
-    fast.PRODUCT = "gemv"
     swiglu = args.swiglu if swiglu is None else swiglu
     x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
@@ -88,21 +86,21 @@ def bench_gemv(args, timer, M=None, N=None, K=None, swiglu=None, name="gemv"):
 
     def fn():
         if args.library:
-            from ..csrc import ops
-            from ..parts.linear import _library_mm
-            y = _library_mm(x, w, torch.float32)
+            y = torch.mm(x, w.t()).float()
             if swiglu:
                 ops.swiglu(y, torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda"))
             return
         if args.tc:
-            from ..csrc import ops
             n = N // 2 if swiglu else N
             parts = 1 if swiglu else ops.gemm_tc_suggest_parts(M, N, K)
             shape = (M, n) if parts == 1 else (parts, M, n)
             ops.gemm_tc(x, w, torch.empty(shape, dtype=out_dtype, device="cuda"), swiglu=swiglu)
             return
-        y = fast.small_batch_linear(x, w, out_dtype, swiglu=swiglu, parts_ok=not swiglu)
-        assert y is not None, "the small-batch product refused these sizes"
+        assert ops.gemv_supported(x, w), "the mma.sync weight streamer refuses these sizes"
+        n = N // 2 if swiglu else N
+        parts = 1 if swiglu else ops.gemv_suggest_parts(M, N, K)
+        shape = (M, n) if parts == 1 else (parts, M, n)
+        ops.gemv_bf16(x, w, torch.empty(shape, dtype=out_dtype, device="cuda"), swiglu=swiglu)
     us = timer.run(fn)
     n_out = N // 2 if swiglu else N
     if args.library:
@@ -136,10 +134,25 @@ def _paged_cache(B, ctx, n_kv, d, page=64, dtype=None):
     return k, v, perm
 
 
+def _decode_splits(B, n_kv, max_len, page, d, fused):
+    """How the attention part cuts the keys of a decoding step (libllm_b200/parts/builtin.cc)."""
+    import torch
+    from ..csrc import ops
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pairs = max(1, B * n_kv)
+    if fused:
+        slots = sms * ops.attention_decode_tc_ctas_per_sm(d)
+        return 0, max(1, min(slots // pairs, max(1, max_len // page)))
+    want = max(1, (8 * sms + pairs - 1) // pairs)
+    n_splits = max(1, min(want, max(1, max_len // (2 * page))))
+    chunk = (max_len + n_splits - 1) // n_splits
+    chunk = (chunk + page - 1) // page * page
+    return chunk, max(1, (max_len + chunk - 1) // chunk)
+
+
 def bench_attention_decode(args, timer):
     import torch
     from ..csrc import ops
-    from ..parts import fast
     B, ctx, nH, nKV, d = args.batch, args.context, args.heads, args.kv_heads, args.head_dim
     k, v, table = _paged_cache(B, ctx, nKV, d)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda")
@@ -148,7 +161,7 @@ def bench_attention_decode(args, timer):
     if args.separate:
         q = torch.randn(B, nH * d, device="cuda").to(torch.bfloat16)
         out = torch.empty_like(q)
-        chunk, n_splits = fast.decode_split(B, nKV, table.shape[1] * 64, 64)
+        chunk, n_splits = _decode_splits(B, nKV, table.shape[1] * 64, 64, d, fused=False)
         ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
         ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
 
@@ -162,7 +175,7 @@ def bench_attention_decode(args, timer):
         ang = torch.arange(ctx + 1, device="cuda", dtype=torch.float64)[:, None] * \
             (10000.0 ** (-torch.arange(0, d, 2, device="cuda", dtype=torch.float64) / d))[None]
         rope = torch.cat([ang.cos(), ang.sin()], 1).float().contiguous()
-        chunk, n_splits = 0, fast.fused_decode_splits(B, nKV, table.shape[1] * 64, 64, d)
+        chunk, n_splits = _decode_splits(B, nKV, table.shape[1] * 64, 64, d, fused=True)
         ws_o = torch.empty(B * nH * n_splits * d, dtype=torch.float32, device="cuda")
         ws_ml = torch.empty(B * nH * n_splits * 2, dtype=torch.float32, device="cuda")
         counters = torch.zeros(B * nKV, dtype=torch.int32, device="cuda")
@@ -179,7 +192,6 @@ def bench_attention_decode(args, timer):
 def bench_attention_prefill(args, timer):
     import torch
     from ..csrc import ops
-    from ..parts import fast
     T, nH, nKV, d = args.tokens, args.heads, args.kv_heads, args.head_dim
     B = args.batch
     k, v, table = _paged_cache(B, T, nKV, d)
@@ -232,7 +244,7 @@ def bench_sampling(args, timer):
 
 
 def bench_gemm(args, timer):
-    """The library product (cuBLAS through torch) that prompts use, for comparison."""
+    """The library product (cuBLAS, here through torch) that prompts use, for comparison."""
     import torch
     M, N, K = args.m, args.n, args.k
     x = torch.randn(M, K, device="cuda").to(torch.bfloat16)

@@ -141,9 +141,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   // every thread: the previous kernel wrote the queries and this step's keys and values
   grid_dependency_wait();
-  const int b = blockIdx.z, h = blockIdx.y;
+  // The grid is [heads, sequences, query tiles]: blocks are handed out with x fastest, so every
+  // head's longest (last) tile starts before anyone's second longest.  Under a causal mask a tile's
+  // work grows with its index; handing out head by head left the last heads' long tiles for the end.
+  const int b = blockIdx.y, h = blockIdx.x;
   const int q0 = seq_start[b], n_q = seq_start[b + 1] - q0, past = seq_past[b];
-  const int tile = gridDim.x - 1 - blockIdx.x;               // long tiles first
+  const int tile = gridDim.z - 1 - blockIdx.z;               // long tiles first
   const int r0 = tile * FT_BM;
   const bool active = r0 < n_q;
   const int rows = active ? min(FT_BM, n_q - r0) : 0;
@@ -504,9 +507,12 @@ attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const _
   const unsigned tmem_base = *tmem_slot;
 
   grid_dependency_wait();
-  const int b = blockIdx.z, h = blockIdx.y;
+  // The grid is [heads, sequences, query tiles]: blocks are handed out with x fastest, so every
+  // head's longest (last) tile starts before anyone's second longest.  Under a causal mask a tile's
+  // work grows with its index; handing out head by head left the last heads' long tiles for the end.
+  const int b = blockIdx.y, h = blockIdx.x;
   const int q0 = seq_start[b], n_q = seq_start[b + 1] - q0, past = seq_past[b];
-  const int tile = gridDim.x - 1 - blockIdx.x;               // long tiles first
+  const int tile = gridDim.z - 1 - blockIdx.z;               // long tiles first
   const int r0 = tile * FW_BM;
   const bool active = r0 < n_q;
   const int rows = active ? min(FW_BM, n_q - r0) : 0;
@@ -827,7 +833,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
     using W = FwShape<D>;
     auto kern = attention_prefill_wide_kernel<D>;
     LLM_CHECK_CUDA(llm_allow_smem(kern, W::SMEM), "attention_prefill_tc attribute");
-    dim3 grid((max_q_len + FW_BM - 1) / FW_BM, n_heads, n_seqs);
+    dim3 grid(n_heads, n_seqs, (max_q_len + FW_BM - 1) / FW_BM);
     LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FW_THREADS), W::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
                               out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window,
                               scale * 1.4426950408889634f, status),
@@ -836,7 +842,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   }
   auto kern = attention_prefill_tc_kernel<D>;
   LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "attention_prefill_tc attribute");
-  dim3 grid((max_q_len + FT_BM - 1) / FT_BM, n_heads, n_seqs);
+  dim3 grid(n_heads, n_seqs, (max_q_len + FT_BM - 1) / FT_BM);
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FT_THREADS), S::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
                             out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window,
                             scale * 1.4426950408889634f, status),
@@ -866,6 +872,7 @@ LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long 
   LLM_REQUIRE(form >= 0 && form <= 2, "attention_prefill_tc: form %d is not one of 0, 1, 2", form);
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv > 0 && n_heads % n_kv == 0,
               "attention_prefill_tc: bad sizes (%d sequences, %d heads, %d kv heads)", n_seqs, n_heads, n_kv);
+  LLM_REQUIRE(max_q_len > 0 && max_q_len <= 65535 * 128, "attention_prefill_tc: %d tokens of one sequence in a step", max_q_len);
   LLM_REQUIRE(llm_attention_prefill_tc_supports(d, page_size),
               "attention_prefill_tc: head size %d with pages of %d tokens is not built (64 or 128, pages of 64)", d, page_size);
   LLM_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)kc % 16 == 0 && (uintptr_t)vc % 16 == 0 &&

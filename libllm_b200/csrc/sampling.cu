@@ -43,9 +43,39 @@ __device__ __forceinline__ ArgMax warp_argmax(ArgMax a) {
 
 __device__ ArgMax block_argmax(const float *row, int V, float *sv, int *si) {
   ArgMax a{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += ST) {
-    ArgMax b{row[i], i};
-    a = better(a, b);
+  if (((uintptr_t)row & 15) == 0) {
+    // Four values a load and four loads in flight: a row of 128,256 logits is 125 dependent
+    // scalar loads a thread otherwise, and the step waits for the slowest row.  The candidates meet
+    // in `better`, which does not depend on the order they come in (ties go to the lower index).
+    const int n4 = V >> 2;
+    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+    int i = threadIdx.x;
+    for (; i + 3 * ST < n4; i += 4 * ST) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = row4[i + u * ST];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = 4 * (i + u * ST);
+        a = better(a, ArgMax{v[u].x, c});
+        a = better(a, ArgMax{v[u].y, c + 1});
+        a = better(a, ArgMax{v[u].z, c + 2});
+        a = better(a, ArgMax{v[u].w, c + 3});
+      }
+    }
+    for (; i < n4; i += ST) {
+      const float4 v = row4[i];
+      a = better(a, ArgMax{v.x, 4 * i});
+      a = better(a, ArgMax{v.y, 4 * i + 1});
+      a = better(a, ArgMax{v.z, 4 * i + 2});
+      a = better(a, ArgMax{v.w, 4 * i + 3});
+    }
+    for (int j = 4 * n4 + threadIdx.x; j < V; j += ST) a = better(a, ArgMax{row[j], j});
+  } else {
+    for (int i = threadIdx.x; i < V; i += ST) {
+      ArgMax b{row[i], i};
+      a = better(a, b);
+    }
   }
   a = warp_argmax(a);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
