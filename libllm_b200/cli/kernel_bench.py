@@ -4,6 +4,7 @@
     python -m libllm_b200.cli.kernel_bench attention_decode --batch 64 --context 2048
     python -m libllm_b200.cli.kernel_bench attention_prefill --tokens 2048
     python -m libllm_b200.cli.kernel_bench layer_products --m 8      # the four products of one layer
+    python -m libllm_b200.cli.kernel_bench chain_layer --m 8         # a layer's products and norms as one launch
 
 One JSON line per run: microseconds per launch (CUDA events on the launching stream,
 after warm-up, with a buffer larger than L2 written between launches), the bytes the
@@ -218,6 +219,76 @@ def bench_attention_prefill(args, timer):
            **({"form": args.form} if use_tc else {}))
 
 
+def bench_chain_layer(args, timer):
+    """A layer's products and norms between two attentions (output projection, add + norm, gate|up +
+    SwiGLU, down, add + norm, q|k|v) as ONE chained launch against the same six as launches of their
+    own, and the times the chained kernel records inside itself (the device's nanosecond clock)."""
+    import ctypes
+    import torch
+    from ..csrc import build, ops
+    T, H, I = args.m, args.hidden, args.intermediate
+    Kq = args.heads * args.head_dim
+    Nq = (args.heads + 2 * args.kv_heads) * args.head_dim
+    bf = torch.bfloat16
+
+    def rnd(shape, std=1.0, dt=bf):
+        return (torch.randn(shape, device="cuda") * std).to(dt)
+    attn, wo, wgu = rnd((T, Kq)), rnd((H, Kq), Kq ** -0.5), rnd((2 * I, H), H ** -0.5)
+    wd, wqkv = rnd((H, I), I ** -0.5), rnd((Nq, H), H ** -0.5)
+    n1, n2 = torch.ones(H, device="cuda"), torch.ones(H, device="cuda")
+    resid = rnd((T, H), dt=torch.float32)
+    po, pd, pq = (ops.gemm_tc_suggest_parts(T, H, Kq), ops.gemm_tc_suggest_parts(T, H, I), ops.gemm_tc_suggest_parts(T, Nq, H))
+    o_parts = torch.empty((po, T, H), dtype=torch.float32, device="cuda")
+    d_parts = torch.empty((pd, T, H), dtype=torch.float32, device="cuda")
+    qkv = torch.empty((pq, T, Nq), dtype=torch.float32, device="cuda")
+    h1, h2 = torch.empty((T, H), dtype=bf, device="cuda"), torch.empty((T, H), dtype=bf, device="cuda")
+    m = torch.empty((T, I), dtype=bf, device="cuda")
+    counters = torch.zeros(16, dtype=torch.int32, device="cuda")
+    jobs = [ops.chain_product(attn, wo, o_parts), ops.chain_norm(resid, o_parts, n1, 1e-5, h1, deps=(0, -1)),
+            ops.chain_product(h1, wgu, m, swiglu=True, deps=(1, -1)), ops.chain_product(m, wd, d_parts, deps=(2, -1)),
+            ops.chain_norm(resid, d_parts, n2, 1e-5, h2, deps=(3, 1)), ops.chain_product(h2, wqkv, qkv, deps=(4, -1))]
+
+    def separate():
+        ops.gemm_tc(attn, wo, o_parts)
+        ops.add_rmsnorm(resid, o_parts, n1, 1e-5, h1)
+        ops.gemm_tc(h1, wgu, m, swiglu=True)
+        ops.gemm_tc(m, wd, d_parts)
+        ops.add_rmsnorm(resid, d_parts, n2, 1e-5, h2)
+        ops.gemm_tc(h2, wqkv, qkv)
+    nbytes = 2 * (wo.numel() + wgu.numel() + wd.numel() + wqkv.numel())
+    report("six launches", timer.run(separate), bytes_moved=nbytes, m=T)
+    report("one chained launch", timer.run(lambda: ops.gemm_chain(jobs, counters)), bytes_moved=nbytes, m=T)
+    # the kernel's own account of one launch
+    names = ["o", "add+norm", "gate|up+swiglu", "down", "add+norm", "q|k|v"]
+    tiles = [((H + 127) // 128) * po, T, (I + 63) // 64, ((H + 127) // 128) * pd, T, ((Nq + 127) // 128) * pq]
+    total = sum(tiles)
+    grid = min(total, torch.cuda.get_device_properties(0).multi_processor_count)
+    trace = torch.zeros(total + 10 * grid + 256, dtype=torch.int64, device="cuda")
+    lib = build.load("gemm_chain")
+    lib.llm_gemm_chain_trace.argtypes = [ctypes.c_void_p]
+    if timer.flusher is not None:
+        timer.flusher.fill_(1)
+    torch.cuda.synchronize()
+    lib.llm_gemm_chain_trace(ctypes.c_void_p(trace.data_ptr()))
+    try:
+        ops.gemm_chain(jobs, counters)
+        torch.cuda.synchronize()
+    finally:
+        lib.llm_gemm_chain_trace(ctypes.c_void_p(0))
+    t = trace.cpu().numpy()
+    per = t[total:total + 10 * grid].reshape(grid, 10)
+    start = int(per[:, 8].min())
+    base, phases = 0, []
+    for j, n in enumerate(tiles):
+        done = t[base:base + n]
+        base += n
+        seen = per[:, j][per[:, j] > 0]
+        phases.append(dict(job=names[j], tiles=n,
+                           inputs_seen_us=[round((int(seen.min()) - start) / 1e3, 2), round((int(seen.max()) - start) / 1e3, 2)] if len(seen) else None,
+                           tiles_done_us=[round((int(done.min()) - start) / 1e3, 2), round((int(done.max()) - start) / 1e3, 2)]))
+    print(json.dumps({"chained launch, times after its first CTA started": phases}), flush=True)
+
+
 def bench_add_rmsnorm(args, timer):
     import torch
     from ..csrc import ops
@@ -255,7 +326,7 @@ def bench_gemm(args, timer):
 
 KERNELS = {"gemv": bench_gemv, "layer_products": bench_layer_products, "attention_decode": bench_attention_decode,
            "attention_prefill": bench_attention_prefill, "add_rmsnorm": bench_add_rmsnorm,
-           "sampling": bench_sampling, "gemm": bench_gemm}
+           "sampling": bench_sampling, "gemm": bench_gemm, "chain_layer": bench_chain_layer}
 
 
 def main(argv=None) -> int:
