@@ -165,13 +165,19 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
   stream.resid = resid;
   stream.rows = T;
   stream.hidden = H;
+  Arena *const step_arena = ctx.arena;
   for (size_t i = 0; i < spec_.schedule.size(); ++i) {
     const ScheduleEntry &e = spec_.schedule[i];
+    if (ctx.layer_arenas[0] && ctx.layer_arenas[1]) {
+      ctx.arena = ctx.layer_arenas[i & 1];
+      ctx.arena->reset();
+    }
     LayerCache lc;
     const bool has_cache = cache.layer_cache((int)i, e.cache_from, tables, table_width, &lc);
     StateView sv = cache.state_view((int)i);
     layers_[(size_t)e.layer]->forward(ctx, stream, has_cache ? &lc : nullptr, sv.empty() ? nullptr : &sv);
   }
+  ctx.arena = step_arena;
   if (ctx.n_want == 0) {
     flush_chain(ctx);
     return Act();

@@ -354,6 +354,8 @@ StepResult Engine::run_eager(const std::vector<StepItem> &items, const SamplingP
   const int W = want_base.back();
   const int64_t V = vocab();
   scratch_.compact();
+  layer_scratch_[0].compact();
+  layer_scratch_[1].compact();
   results_.compact();
   results_.reset();
   float *all_logits = W ? results_.alloc_n<float>((size_t)W * (size_t)V) : nullptr;
@@ -393,6 +395,8 @@ StepResult Engine::run_eager(const std::vector<StepItem> &items, const SamplingP
     std::vector<const int *> tables;
     scratch_.reset();
     StepContext ctx = context(d, pieces, (int)want_rows.size(), all_single, max_kv, &scratch_, &tables);
+    ctx.layer_arenas[0] = &layer_scratch_[0];
+    ctx.layer_arenas[1] = &layer_scratch_[1];
     Act logits = model_->forward(ctx, *cache_, tables, width, last_tokens_.as<int>(), d.dev(Descriptor::Fed));
     int *chunk_tokens = nullptr;
     if (sampling && !want_rows.empty()) {

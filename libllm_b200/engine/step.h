@@ -162,7 +162,7 @@ class Engine {
   std::unique_ptr<KVCache> cache_;
   cudaStream_t stream_ = nullptr;
   int sm_count_ = 148;
-  Arena scratch_, results_;
+  Arena scratch_, results_, layer_scratch_[2];
   DeviceBuffer status_, counters_, last_tokens_;
   std::unique_ptr<Chain> chain_;     // the queue of the step being launched (parts/chain.h)
   int last_capacity_ = 0;

@@ -109,6 +109,10 @@ struct StepContext {
   bool decode_only = false;          // every sequence brings exactly one token
   bool captured = false;
   Arena *arena = nullptr;            // device memory that lives until the step's results are read
+  // When set, the model gives every layer one of these two in turn, emptied first: what a layer
+  // allocates has to outlive the layer after it (the pending residual addition) and no more.  A
+  // prompt step of thousands of tokens then holds two layers' activations, not all layers'.
+  Arena *layer_arenas[2] = {nullptr, nullptr};
   int *tc_status = nullptr;          // the word in which tensor-core kernels record a wait that ran out
   int *zero_counters = nullptr;      // int32 zeros that kernels may count in if they leave them zero
   int n_zero_counters = 0;
