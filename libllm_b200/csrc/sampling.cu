@@ -21,6 +21,8 @@ LLM_DEFINE_LAST_ERROR(llm_sampling_last_error)
 
 constexpr int ST = 1024;         // threads per row
 constexpr int MAX_TOP_K = 1024;
+constexpr int MAX_CAND = 2048;   // candidates the quick selection sorts; more: the radix selection
+constexpr int SEL_BINS = 256;    // bins of the quick selection, 1/32 wide in (max - logit) / temperature
 
 struct ArgMax {
   float v;
@@ -178,7 +180,8 @@ sample_kernel(const float *__restrict__ logits, long long stride, int V, float t
   __shared__ unsigned hist[256];
   __shared__ unsigned sel_prefix, sel_mask;
   __shared__ int sel_remaining, n_greater, result;
-  __shared__ unsigned long long cand[MAX_TOP_K];
+  __shared__ unsigned long long cand[MAX_CAND];
+  __shared__ int sel_bin, n_cand;
   grid_dependents_launch();
   grid_dependency_wait();
 
@@ -196,10 +199,44 @@ sample_kernel(const float *__restrict__ logits, long long stride, int V, float t
   const int chunk = (V + ST - 1) / ST;
   const int c0 = min(V, tid * chunk), c1 = min(V, c0 + chunk);
 
+  // With top_k the sum is only the normaliser: one pass with every thread striding over the row
+  // (four values a load when the row allows) sums the exponentials and counts, in bins of
+  // (max - logit) / temperature, the logits within 8 of the maximum.  The candidates are then the
+  // logits in the bins up to the one where the count reaches top_k; sorted, their first top_k are
+  // the top_k of the row.  Seven passes of one block over half a megabyte become three.  Flat rows
+  // (more than MAX_CAND candidates, or fewer than top_k logits within 8 of the maximum) take the
+  // radix selection below, which is exact for any row.
   float part = 0.f;
-  for (int i = c0; i < c1; ++i) part += expf((row[i] - mx) * inv_t);
+  const int k = min(top_k, V);
+  bool quick = false;
+  if (top_k > 0) {
+    if (tid < SEL_BINS) hist[tid] = 0u;
+    __syncthreads();
+    auto take = [&](float x) {
+      const float d = (mx - x) * inv_t;
+      part += expf((x - mx) * inv_t);
+      const int bin = (int)(d * 32.f);
+      if (d >= 0.f && bin < SEL_BINS) atomicAdd(&hist[bin], 1u);
+    };
+    if (((uintptr_t)row & 15) == 0) {
+      const int n4 = V >> 2;
+      const float4 *row4 = reinterpret_cast<const float4 *>(row);
+      for (int i = tid; i < n4; i += ST) {
+        const float4 v = row4[i];
+        take(v.x);
+        take(v.y);
+        take(v.z);
+        take(v.w);
+      }
+      for (int j = 4 * n4 + tid; j < V; j += ST) take(row[j]);
+    } else {
+      for (int i = tid; i < V; i += ST) take(row[i]);
+    }
+  } else {
+    for (int i = c0; i < c1; ++i) part += expf((row[i] - mx) * inv_t);
+  }
   float Z;
-  const float before = block_exclusive_scan(part, fscan, &Z);
+  const float before = block_exclusive_scan(part, fscan, &Z);     // also a barrier: the counts are complete
 
   if (top_k == 0) {
     const float r = u * Z;
@@ -224,8 +261,47 @@ sample_kernel(const float *__restrict__ logits, long long stride, int V, float t
     return;
   }
 
-  // ---- the top_k-th largest logit by radix selection over order-preserving keys
-  const int k = min(top_k, V);
+  // ---- the quick selection: the bin where the count reaches top_k, and what lies up to it
+  if (tid == 0) {
+    int cum = 0, b = 0;
+    for (; b < SEL_BINS; ++b) {
+      cum += (int)hist[b];
+      if (cum >= k) break;
+    }
+    sel_bin = (b < SEL_BINS && cum <= MAX_CAND) ? b : -1;
+    n_cand = 0;
+  }
+  __syncthreads();
+  quick = sel_bin >= 0;
+  int n_sort = k;
+  if (quick) {
+    const int last = sel_bin;
+    auto keep = [&](float x, int i) {
+      const float d = (mx - x) * inv_t;
+      if (d >= 0.f && (int)(d * 32.f) <= last) {
+        const int s = atomicAdd(&n_cand, 1);
+        cand[s] = ((unsigned long long)ordered_key(x) << 32) | (unsigned)(0xffffffffu - (unsigned)i);
+      }
+    };
+    if (((uintptr_t)row & 15) == 0) {
+      const int n4 = V >> 2;
+      const float4 *row4 = reinterpret_cast<const float4 *>(row);
+      for (int i = tid; i < n4; i += ST) {
+        const float4 v = row4[i];
+        keep(v.x, 4 * i);
+        keep(v.y, 4 * i + 1);
+        keep(v.z, 4 * i + 2);
+        keep(v.w, 4 * i + 3);
+      }
+      for (int j = 4 * n4 + tid; j < V; j += ST) keep(row[j], j);
+    } else {
+      for (int i = tid; i < V; i += ST) keep(row[i], i);
+    }
+    __syncthreads();
+    n_sort = n_cand;
+  }
+  // ---- otherwise the top_k-th largest logit by radix selection over order-preserving keys
+  if (!quick) {
   if (tid == 0) { sel_prefix = 0u; sel_mask = 0u; sel_remaining = k; }
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
@@ -276,10 +352,11 @@ sample_kernel(const float *__restrict__ logits, long long stride, int V, float t
       }
     }
   }
-  // ---- sort the k candidates: value falling, index rising on ties (bitonic, padded)
+  }  // radix selection
+  // ---- sort the candidates: value falling, index rising on ties (bitonic, padded)
   int n = 1;
-  while (n < k) n <<= 1;
-  for (int i = k + tid; i < n; i += ST) cand[i] = 0ull;
+  while (n < n_sort) n <<= 1;
+  for (int i = n_sort + tid; i < n; i += ST) cand[i] = 0ull;
   __syncthreads();
   for (int size = 2; size <= n; size <<= 1) {
     for (int strd = size >> 1; strd > 0; strd >>= 1) {

@@ -249,6 +249,37 @@ def test_sampling_matches_plain_sampler(vocab, temperature, top_k, top_p):
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("case", ["flat", "many_tied_leaders", "ties_at_the_kth", "none_near_the_maximum"])
+def test_sampling_rows_that_the_quick_selection_must_get_right_or_hand_on(case):
+    """Rows at the edges of the two ways the kernel finds the top_k: all logits equal and thousands
+    of tied leaders (more candidates than the quick selection sorts), ties exactly at the k-th place
+    inside it (the lower indices are taken), and fewer than top_k logits near the maximum."""
+    from libllm_b200.csrc import ops
+    V, top_k = 20000, 50
+    g = torch.Generator().manual_seed(23)
+    if case == "flat":
+        row = torch.full((V,), 1.5)
+    elif case == "many_tied_leaders":
+        row = torch.randn(V, generator=g) - 30.0
+        row[torch.randperm(V, generator=g)[:3000]] = 4.0
+    elif case == "ties_at_the_kth":
+        row = torch.randn(V, generator=g) - 40.0
+        idx = torch.randperm(V, generator=g)
+        row[idx[:10]] = torch.linspace(5.0, 6.0, 10)
+        row[idx[10:1510]] = 4.0
+    else:
+        row = torch.randn(V, generator=g) * 0.1 - 50.0
+        row[torch.randperm(V, generator=g)[:7]] = torch.linspace(1.0, 3.0, 7)
+    us = [0.0, 0.21, 0.5, 0.83, 0.97, 0.9999]
+    logits = row.to(DEV).repeat(len(us), 1).contiguous()
+    uni = torch.tensor(us, dtype=torch.float32, device=DEV)
+    out = torch.empty(len(us), dtype=torch.int32, device=DEV)
+    for temperature, top_p in ((1.0, 1.0), (0.7, 0.9)):
+        ops.sample(logits, temperature, top_k, top_p, uni, out)
+        for i, u in enumerate(us):
+            assert _interval_ok(row, temperature, top_k, top_p, u, int(out[i])), (case, temperature, top_p, u, int(out[i]))
+
+
 def test_kernels_refuse_what_they_cannot_do():
     from libllm_b200.csrc import ops
     from libllm_b200.errors import ExtensionError, UnsupportedError
