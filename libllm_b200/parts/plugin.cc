@@ -264,7 +264,7 @@ class PluginPosition : public PositionEncoding {
 
 // ---------------------------------------------------------------- the C entry points
 namespace llm {
-int guard_api(const std::function<void()> &body);     // api/llm_api.cc: runs body, keeps an error's message, returns its status
+int guard_api(const std::function<void()> &body);     // capi/llm_api.cc: runs body, keeps an error's message, returns its status
 }
 
 extern "C" __attribute__((visibility("default"))) int32_t llm_register_part(const char *category, const char *kind,

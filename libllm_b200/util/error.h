@@ -1,6 +1,6 @@
 // Errors of the host library.  Every failure inside the library is an `llm::Error` that carries
 // the reference's status number (src/libllm/llm.h:42-45) and a finer kind; the C API
-// (libllm_b200/api/llm_api.cc) catches it at the boundary and keeps the message for
+// (libllm_b200/capi/llm_api.cc) catches it at the boundary and keeps the message for
 // `llm_get_last_error_message`, as the reference does (src/libllm/llm.cc:60-71).
 #pragma once
 #include <cstdarg>
