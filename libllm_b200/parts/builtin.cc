@@ -446,10 +446,23 @@ class PreNormBlock : public Block {
     return true;
   }
   void forward(StepContext &ctx, ResidualStream &stream, LayerCache *cache, StateView *state) override {
+    // After a norm the stream holds everything added so far, so a part may add its result to it
+    // directly (StepContext::residual_sink); what it returns otherwise stays pending for the next norm.
+    auto sink = [&](bool on) {
+      ctx.residual_sink = on ? stream.resid : nullptr;
+      ctx.sink_rows = stream.rows;
+      ctx.sink_cols = stream.hidden;
+    };
     Act h = mixer_norm_->forward(ctx, stream);
-    stream.pending = mixer_->forward(ctx, h, cache, state);
+    sink(true);
+    Act r = mixer_->forward(ctx, h, cache, state);
+    sink(false);
+    stream.pending = r.data == (void *)stream.resid ? Act() : r;
     h = ff_norm_->forward(ctx, stream);
-    stream.pending = ff_->forward(ctx, h);
+    sink(true);
+    r = ff_->forward(ctx, h);
+    sink(false);
+    stream.pending = r.data == (void *)stream.resid ? Act() : r;
   }
 
  private:

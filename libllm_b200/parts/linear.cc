@@ -29,6 +29,7 @@ const FastSwitches &fast_switches() {
     f.decode_attention_tc = !off("LIBLLM_B200_NO_DECODE_ATTENTION_TC");
     f.library_gemm = !off("LIBLLM_B200_NO_LIBRARY_GEMM");
     f.gemm_chain = off("LIBLLM_B200_GEMM_CHAIN");      // set: on (measured no faster than the launches it replaces)
+    f.add_in_product = !off("LIBLLM_B200_NO_ADD_IN_PRODUCT");
     f.tc_tokens = num("LIBLLM_B200_TC_TOKENS", 256);
     f.fused_gate_up_tokens = num("LIBLLM_B200_FUSED_GATE_UP_TOKENS", 1024);
     f.gemv_tokens = num("LIBLLM_B200_GEMV_TOKENS", 0);
@@ -96,7 +97,7 @@ bool library_gemm_available() {
   return fast_switches().library_gemm && open_cublas(c);
 }
 
-bool library_gemm(cudaStream_t stream, const Act &x, const Weight &w, const Act &out) {
+bool library_gemm(cudaStream_t stream, const Act &x, const Weight &w, const Act &out, bool accumulate) {
   Cublas &c = cublas();
   std::lock_guard<std::mutex> g(c.mu);
   if (!fast_switches().library_gemm || !open_cublas(c)) return false;
@@ -115,7 +116,7 @@ bool library_gemm(cudaStream_t stream, const Act &x, const Weight &w, const Act 
   if (c.set_stream(h, stream) != CUBLAS_STATUS_SUCCESS) LLM_THROW(Extension, "cublasSetStream failed");
   if (c.set_workspace(h, c.workspaces[dev].get(), c.workspaces[dev].bytes()) != CUBLAS_STATUS_SUCCESS)
     LLM_THROW(Extension, "cublasSetWorkspace failed");
-  const float alpha = 1.f, beta = 0.f;
+  const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
   // Row-major out[T, N] = x[T, K] w[N, K]^T is, column-major, out^T[N, T] = w^T(op T)[N, K] x^T[K, T].
   const cublasStatus_t st =
       c.gemm_ex(h, CUBLAS_OP_T, CUBLAS_OP_N, (int)w.rows, (int)x.rows, (int)x.cols, &alpha, w.data(), CUDA_R_16BF, (int)w.cols,
@@ -165,8 +166,20 @@ Act linear(StepContext &ctx, const Act &x, const Weight &w, const float *bias, D
   }
   Act y = small_batch_linear(ctx, x, w, out_dtype, false, parts_ok);
   if (y.data) return y;
+  const bool lib_ok = x.cols % 8 == 0 && (uintptr_t)x.data % 16 == 0;
+  if (parts_ok && lib_ok && out_dtype == DType::F32 && ctx.residual_sink && ctx.sink_rows == T && ctx.sink_cols == w.rows &&
+      fast_switches().add_in_product) {
+    // the residual addition rides on the product's store: one pass over the stream less per norm
+    Act sink;
+    sink.data = ctx.residual_sink;
+    sink.dtype = DType::F32;
+    sink.rows = T;
+    sink.cols = sink.ld = w.rows;
+    sink.part_stride = sink.rows * sink.cols;
+    if (library_gemm(ctx.stream, x, w, sink, true)) return sink;
+  }
   Act out = ctx.arena->act(out_dtype, T, w.rows);
-  if (x.cols % 8 == 0 && (uintptr_t)x.data % 16 == 0 && library_gemm(ctx.stream, x, w, out)) return out;
+  if (lib_ok && library_gemm(ctx.stream, x, w, out)) return out;
   if (fast_switches().gemm_tc && kernels::gemm_tc_supported(x, w)) {
     kernels::gemm_tc(x, w, out, false, ctx.tc_status, ctx.stream);
     return out;

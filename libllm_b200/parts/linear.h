@@ -14,6 +14,7 @@ namespace llm {
 struct FastSwitches {
   bool gemm_tc = true, gemv = true, decode_attention = true, prefill_attention = true, prefill_attention_tc = true,
        decode_attention_tc = true, library_gemm = true;
+  bool add_in_product = true;          // prompt steps: the library product adds its result to the residual stream itself
   bool gemm_chain = false;             // queue a decoding step's products and norms into single launches (parts/chain.h)
   int tc_tokens = 256;                 // steps of up to this many tokens take the tcgen05 product
   int fused_gate_up_tokens = 1024;     // prompt steps from this many tokens fuse SwiGLU into the product ...
@@ -27,7 +28,9 @@ std::vector<std::string> product_families(DType dtype);
 
 // x [T, K] in the engine's type, w [N, K]; returns [T, N] in out_dtype.  With parts_ok (for
 // results that go into the residual addition, which adds parts in order) the result may be
-// [parts, T, N] partial products to be summed.
+// [parts, T, N] partial products to be summed, or, when the block has named the residual
+// stream's rows (StepContext::residual_sink) and the library product runs, the stream itself with
+// the result already added to it.
 Act linear(StepContext &ctx, const Act &x, const Weight &w, const float *bias, DType out_dtype, bool parts_ok = false);
 
 // The product for steps of few tokens; data == nullptr when it does not take the case.  With
@@ -36,7 +39,8 @@ Act small_batch_linear(StepContext &ctx, const Act &x, const Weight &w, DType ou
 
 // out[T, N] = x[T, K] @ w[N, K]^T by cuBLAS (bfloat16 operands, 32-bit accumulation); false when
 // the library is not to be had.
-bool library_gemm(cudaStream_t stream, const Act &x, const Weight &w, const Act &out);
+// With `accumulate` the product is added to what `out` holds (32-bit out).
+bool library_gemm(cudaStream_t stream, const Act &x, const Weight &w, const Act &out, bool accumulate = false);
 bool library_gemm_available();
 
 }  // namespace llm

@@ -120,6 +120,12 @@ struct StepContext {
   // When set, products and norms are queued and launched together (parts/chain.h).  Whoever
   // launches anything else on `stream`, or hands a buffer to code outside, calls flush_chain() first.
   Chain *chain = nullptr;
+  // Set by a block around its mixer and its feed-forward: the rows of the 32-bit residual stream that
+  // the part's result will be added to.  A part whose last product can add to them as it stores
+  // (the library product of a prompt step, with its beta) does so and returns an Act whose data IS
+  // this pointer; the block then has nothing left to add.  Parts that ignore it lose nothing.
+  float *residual_sink = nullptr;
+  int64_t sink_rows = 0, sink_cols = 0;
 };
 
 // Device memory for a step's activations: handed out front to back, taken back all at once.

@@ -41,6 +41,22 @@ def test_each_request_alone_and_whole(name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_prompts_of_hundreds_of_tokens(name, dtype):
+    """Prompt steps above the token count where the products change hands (the library's product,
+    which adds its result to the residual stream as it stores): one prompt alone, then two of unequal
+    lengths in one step, each followed by a few single tokens."""
+    engine, c, w = setup(name, dtype)
+    toks = tokens_for(name, 420, 61)
+    got = replay_batch(engine, [("r", toks, 417)])["r"]
+    check_against_plain(got, c, w, toks, dtype, f"{name} prompt of 417")
+    reqs = [("long", tokens_for(name, 303, 62), 300), ("short", tokens_for(name, 95, 63), 90)]
+    got = replay_batch(engine, reqs)
+    for rid, toks, _ in reqs:
+        check_against_plain(got[rid], c, w, toks, dtype, f"{name} {rid} beside the other")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_last_32_tokens_one_by_one(name, dtype):
     engine, c, w = setup(name, dtype)
     for i, n in enumerate([33, 100, 160]):
