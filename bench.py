@@ -322,7 +322,16 @@ def main():
                     help="1b: the benchmark line (default); 3b, 8b: the larger workloads, a line of their own")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling; not a bench record)")
+    ap.add_argument("--prompt-len", type=int, default=None,
+                    help="with --only: prompts of this many tokens instead of 2048 (the context grows to fit)")
     args = ap.parse_args()
+    if args.prompt_len:
+        if not args.only:
+            print("bench.py: --prompt-len goes with --only (the record is taken at the sizes BASELINE.json names)")
+            return 2
+        global PROMPT, CONTEXT
+        PROMPT = args.prompt_len
+        CONTEXT = max(CONTEXT, PROMPT + 2048)
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:
@@ -346,8 +355,9 @@ def main():
 
     if args.only == "decode":
         rate, ms, ctx_len, _ = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+        step_bytes = wbytes + args.batch * ctx_len * kv_per_tok
         print(json.dumps({"only": "decode", "batch": args.batch, "tok_s": round(rate, 1), "ms_per_step": round(ms, 4),
-                          "context": ctx_len}))
+                          "context": ctx_len, "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}))
         return 0
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", **prefill_rate(model, vocab, flops_fn, pk["bf16_tflops"])}))

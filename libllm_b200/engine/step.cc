@@ -380,7 +380,8 @@ StepResult Engine::run_eager(const std::vector<StepItem> &items, const SamplingP
       }
       o += p.count;
       max_kv = std::max(max_kv, p.past + p.start + p.count);
-      need_pages = std::max(need_pages, (p.past + p.start + p.count + opt_.page_size - 1) / opt_.page_size);
+      // every page the slot holds: the step's pages were all taken before its first launch sequence
+      need_pages = std::max(need_pages, cache_->pages_needed(p.slot));
     }
     const int width = std::max(8, (need_pages + 7) / 8 * 8);
     Descriptor &d = *eager_desc_[eager_turn_];

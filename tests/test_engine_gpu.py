@@ -122,6 +122,11 @@ def test_prompt_cut_into_chunks(dtype):
     got = replay_batch(engine, reqs)
     for rid, toks, _ in reqs:
         check_against_plain(got[rid], c, w, toks, dtype, f"chunked {rid}")
+    # a prompt whose pages outnumber the page table of its first launch sequences (the step takes all
+    # its pages before the first of them runs)
+    toks = tokens_for("C", 702, 3)
+    got = replay_batch(engine, [("long", toks, 700)])["long"]
+    check_against_plain(got, c, w, toks, dtype, "chunked prompt of 700")
 
 
 def test_batch_composition_does_not_change_float32_results():
