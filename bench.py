@@ -106,6 +106,56 @@ def model_numbers(c):
     return weight_bytes, kv_bytes_per_token, prefill_flops
 
 
+LAST_STEP_TIMES = []          # milliseconds of each timed step of the last decode_rate call
+
+
+def products_alone(cfg, tokens, pk):
+    """The step's dominant kernel by itself: the tcgen05 products of a whole step (every layer's four,
+    each layer with weights of its own so that none is met in L2, then the output matrix) launched one
+    behind the other as in the step (one CUDA graph), without the attention and the norms between them: bytes of weights
+    over time against the measured bandwidth.  What the step loses beyond this is the other kernels
+    and the hand-overs to and from them."""
+    import torch
+    from libllm_b200.csrc import ops
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nH, nKV, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    bf = torch.bfloat16
+    shapes = [((nH + 2 * nKV) * d, H, False), (H, nH * d, False), (2 * I, H, True), (H, I, False)]
+    jobs, nbytes = [], 0.0
+    for layer in range(L + 1):
+        for n, k, sw in (shapes if layer < L else [(V, H, False)]):
+            x = torch.randn(tokens, k, device="cuda").to(bf)
+            w = torch.empty(n, k, device="cuda", dtype=bf).normal_(0.0, 0.02)
+            n_out = n // 2 if sw else n
+            parts = 1 if sw or n == V else ops.gemm_tc_suggest_parts(tokens, n, k)
+            out = torch.empty((tokens, n_out) if parts == 1 else (parts, tokens, n_out), dtype=bf if sw else torch.float32, device="cuda")
+            jobs.append((x, w, out, sw))
+            nbytes += 2.0 * n * k
+    def run():
+        for x, w, out, sw in jobs:
+            ops.gemm_tc(x, w, out, swiglu=sw)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        run()                                    # outside capture once: attributes, tensor maps
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            run()
+        times = []
+        for rep in range(6):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            graph.replay()
+            b.record(side)
+            b.synchronize()
+            if rep >= 2:
+                times.append(a.elapsed_time(b) * 1e3)
+    us = statistics.median(times)
+    gbs = nbytes / (us * 1e-6) / 1e9
+    return {"kernel": "gemm_tc_kernel: the step's products one behind the other, nothing between them",
+            "launches": len(jobs), "us_per_step": round(us, 1), "gb_s": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 4)}
+
+
 def decode_rate(model, batch, steps, warmup, vocab, seed=0):
     """Decoded tokens a second at ``batch`` with the steps timed on the device: CUDA events on the
     engine's stream around ``steps`` decode steps that are queued one behind the other (each takes
@@ -129,15 +179,18 @@ def decode_rate(model, batch, steps, warmup, vocab, seed=0):
         launches = (_lib.lib().llm_kernel_launches() - n0) // 2
         for _ in range(max(warmup - 1, 2)):
             eng.step_tokens(fed, GREEDY).result()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         eng.synchronize()
-        start.record(stream)
-        pending = [eng.step_tokens(fed, GREEDY) for _ in range(steps)]
-        end.record(stream)
+        marks[0].record(stream)
+        pending = []
+        for i in range(steps):
+            pending.append(eng.step_tokens(fed, GREEDY))
+            marks[i + 1].record(stream)
         for p in pending:
             p.result()
         eng.synchronize()
-        ms = start.elapsed_time(end) / steps
+        ms = marks[0].elapsed_time(marks[steps]) / steps          # the K steps as one stretch: the record's figure
+        LAST_STEP_TIMES[:] = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
         ctx_len = eng.sequence_length(slots[0])
         return batch * 1000.0 / ms, ms, ctx_len, launches
     finally:
@@ -366,6 +419,8 @@ def main():
     sampler.start()
     rate, ms, ctx_len, launches_per_step = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
     clocks = sampler.stop()
+    step_times = sorted(LAST_STEP_TIMES)
+    median_ms = step_times[len(step_times) // 2] if step_times else ms
     e2e, h2d, d2h = e2e_rate(model, args.batch, args.steps, args.warmup, vocab)
     prefill = prefill_rate(model, vocab, flops_fn, pk["bf16_tflops"])
     step_bytes = wbytes + args.batch * ctx_len * kv_per_tok
@@ -378,8 +433,8 @@ def main():
     line = {
         "metric": "decode tok/s (Llama-3.2-1B layer sizes, batch 8, 2048-token prompts, 4096 context)",
         "value": round(rate, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "ms_per_step": round(ms, 4), "ms_per_step_median": round(median_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {"model": "llama-3.2-1b-sizes", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
@@ -394,6 +449,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "dominant_kernel": products_alone(cfg, args.batch, pk),
     }
     print(json.dumps(line))
     return 0
