@@ -100,7 +100,9 @@ def model_numbers(c):
     kv_bytes_per_token = 2 * L * nKV * d * 2
 
     def prefill_flops(T, rows=1):
-        lin = 2 * T * L * (H * (nH + 2 * nKV) * d + nH * d * H + 3 * H * I)
+        # what the step has to compute: the last layer's feed-forward and the output matrix only for
+        # the rows whose logits are wanted (the engine does no more, so no more is counted)
+        lin = 2 * T * L * (H * (nH + 2 * nKV) * d + nH * d * H) + 2 * (T * (L - 1) + rows) * 3 * H * I
         att = L * 4 * nH * d * T * (T + 1) // 2            # q k^T and p v over the causal half
         return lin + att + 2 * rows * V * H
     return weight_bytes, kv_bytes_per_token, prefill_flops

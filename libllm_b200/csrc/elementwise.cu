@@ -263,6 +263,37 @@ LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype,
   LLM_FAIL("add_rmsnorm: unknown dtypes %d, %d", delta_dtype, out_dtype);
 }
 
+// ---------------------------------------------------------------- rows of the stream picked out
+// out[i] = resid[rows[i]] + sum_p delta[p][rows[i]] (32-bit, parts in index order): the residual
+// stream of the rows that anything still reads, when the others are done with.
+template <typename TD>
+__global__ void gather_rows_add_kernel(const float *__restrict__ resid, const TD *__restrict__ delta, int n_parts,
+                                       size_t part_stride, const int *__restrict__ rows, float *__restrict__ out, int hidden) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int i = blockIdx.x;
+  const size_t r = (size_t)rows[i];
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = resid[r * hidden + c];
+    for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + r * hidden + c]);
+    out[(size_t)i * hidden + c] = v;
+  }
+}
+
+LLM_EXPORT int llm_gather_rows_add(const float *resid, const void *delta, int delta_dtype, int n_parts, long long part_stride,
+                                   const int *rows, int n_rows, float *out, int hidden, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 0 && rows != nullptr && out != nullptr, "gather_rows_add: bad arguments");
+  if (!delta) n_parts = 0;
+  if (delta_dtype == LLM_BF16 && n_parts > 0)
+    LLM_CHECK_CUDA(llm_launch(gather_rows_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, resid, (const __nv_bfloat16 *)delta,
+                              n_parts, (size_t)part_stride, rows, out, hidden), "gather_rows_add launch");
+  else
+    LLM_CHECK_CUDA(llm_launch(gather_rows_add_kernel<float>, dim3(n_rows), dim3(256), 0, stream, resid, (const float *)delta, n_parts,
+                              (size_t)part_stride, rows, out, hidden), "gather_rows_add launch");
+  return LLM_OK;
+}
+
 // ---------------------------------------------------------------- swiglu
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(a) = a / (1 + exp(-a)).  TI is the
 // type of the stacked gate|up product (32-bit when the product gives that), T of out.

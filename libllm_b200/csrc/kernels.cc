@@ -142,6 +142,7 @@ LLM_KERNEL("elementwise", llm_copy_words, const int *, int *, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_gather_words, const int *, int, const int *, int, int *, cudaStream_t)
 LLM_KERNEL("elementwise", llm_add_rmsnorm, float *, const void *, int, int, long long, const float *, float, void *, int,
            const int *, int, int, cudaStream_t)
+LLM_KERNEL("elementwise", llm_gather_rows_add, const float *, const void *, int, int, long long, const int *, int, float *, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_swiglu, int, int, const void *, void *, int, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_scale_rows, float *, long long, float, cudaStream_t)
 LLM_KERNEL("elementwise", llm_logit_transform, float *, long long, float, float, cudaStream_t)
@@ -161,6 +162,11 @@ void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps,
   LLM_CALL("elementwise", llm_add_rmsnorm, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
            has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, eps, out, code(out_dtype), rows, n_rows,
            hidden, s);
+}
+void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s) {
+  const bool has = delta && delta->data;
+  LLM_CALL("elementwise", llm_gather_rows_add, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0, has ? delta->parts : 0,
+           has ? (long long)delta->part_stride : 0, rows, n_rows, out, hidden, s);
 }
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s) {
   LLM_CALL("elementwise", llm_swiglu, code(gu.dtype), code(out_dtype), gu.data, out, (int)gu.rows, (int)(gu.cols / 2), s);

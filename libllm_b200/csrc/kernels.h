@@ -31,6 +31,8 @@ void copy_words(const int *src, int *dst, int n, cudaStream_t s);
 void gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cudaStream_t s);
 void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps, void *out, DType out_dtype,
                  const int *rows, int n_rows, int hidden, cudaStream_t s);
+// out[i] = resid[rows[i]] + delta's parts at that row (32-bit)
+void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s);
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s);
 void scale_rows(float *x, long long n, float scale, cudaStream_t s);
 void logit_transform(float *logits, long long n, float scale, float softcap, cudaStream_t s);

@@ -172,6 +172,9 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
       ctx.arena = ctx.layer_arenas[i & 1];
       ctx.arena->reset();
     }
+    const bool last = i + 1 == spec_.schedule.size();
+    ctx.rows_read_after = last && ctx.n_want > 0 && ctx.n_want < ctx.n_tokens ? ctx.want_rows : nullptr;
+    ctx.n_rows_read_after = ctx.rows_read_after ? ctx.n_want : 0;
     LayerCache lc;
     const bool has_cache = cache.layer_cache((int)i, e.cache_from, tables, table_width, &lc);
     StateView sv = cache.state_view((int)i);
@@ -182,7 +185,8 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
     flush_chain(ctx);
     return Act();
   }
-  Act h = final_norm_->forward(ctx, stream, ctx.want_rows, ctx.n_want);
+  ctx.rows_read_after = nullptr;
+  Act h = stream.picked ? final_norm_->forward(ctx, stream) : final_norm_->forward(ctx, stream, ctx.want_rows, ctx.n_want);
   Act logits = linear(ctx, h, *head_, nullptr, DType::F32);
   flush_chain(ctx);
   if (spec_.logit_scale != 1.0 || spec_.logit_softcap > 0.0)

@@ -458,6 +458,18 @@ class PreNormBlock : public Block {
     Act r = mixer_->forward(ctx, h, cache, state);
     sink(false);
     stream.pending = r.data == (void *)stream.resid ? Act() : r;
+    if (ctx.rows_read_after && ctx.n_rows_read_after < stream.rows && !stream.picked) {
+      // the last layer of a prompt step: the feed-forward of the wanted rows alone
+      flush_chain(ctx);
+      const int64_t n = ctx.n_rows_read_after;
+      float *few = ctx.arena->alloc_n<float>((size_t)(n * stream.hidden));
+      kernels::gather_rows_add(stream.resid, stream.pending.data ? &stream.pending : nullptr, ctx.rows_read_after, (int)n, few,
+                               (int)stream.hidden, ctx.stream);
+      stream.resid = few;
+      stream.rows = n;
+      stream.pending = Act();
+      stream.picked = true;
+    }
     h = ff_norm_->forward(ctx, stream);
     sink(true);
     r = ff_->forward(ctx, h);

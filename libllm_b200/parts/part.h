@@ -126,6 +126,12 @@ struct StepContext {
   // this pointer; the block then has nothing left to add.  Parts that ignore it lose nothing.
   float *residual_sink = nullptr;
   int64_t sink_rows = 0, sink_cols = 0;
+  // Set by the model for the last layer of a step that wants the logits of fewer rows than it has
+  // tokens (a prompt whose last token alone is wanted): after that layer's mixer nothing but these
+  // rows of the residual stream is read.  A block may then go on with those rows alone
+  // (ResidualStream::picked); one that ignores it computes all rows as before.
+  const int *rows_read_after = nullptr;
+  int n_rows_read_after = 0;
 };
 
 // Device memory for a step's activations: handed out front to back, taken back all at once.
@@ -157,6 +163,7 @@ struct ResidualStream {
   float *resid = nullptr;
   int64_t rows = 0, hidden = 0;
   Act pending;                       // data == nullptr: nothing pending
+  bool picked = false;               // the rows are StepContext::rows_read_after, in that order, and no others
 };
 
 // What load() fetches tensors through: the files of a model folder, tensors in host memory, or

@@ -196,6 +196,27 @@ def test_wanted_places_in_any_order_across_pieces():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_prompt_whose_last_row_alone_is_wanted(name, dtype):
+    """The step a generation starts with: the last layer then runs its feed-forward for the wanted
+    rows alone.  One row, a row wanted twice beside others, and two prompts of unequal lengths; then a
+    token more for each, which reads the keys and values the prompt step left in every layer."""
+    from libllm_b200.engine import StepItem
+    engine, c, w = setup(name, dtype)
+    a, b = tokens_for(name, 301, 71), tokens_for(name, 41, 72)
+    ref_a, ref_b = plain(c, w, a), plain(c, w, b)
+    sa, sb = engine.open_sequence(), engine.open_sequence()
+    got = torch.from_numpy(engine.step([StepItem(sa, a[:300], [299]), StepItem(sb, b[:40], [39, 7, 39])]))
+    check_logits(got[:1], ref_a[[299]], dtype, "last row of a")
+    check_logits(got[1:], ref_b[[39, 7, 39]], dtype, "rows of b")
+    got = torch.from_numpy(engine.step([StepItem(sa, a[300:], [0]), StepItem(sb, b[40:], [0])]))
+    check_logits(got[:1], ref_a[[300]], dtype, "a's next token")
+    check_logits(got[1:], ref_b[[40]], dtype, "b's next token")
+    engine.close_sequence(sa)
+    engine.close_sequence(sb)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_tensors_stored_in_other_types_load_to_the_same_model(dtype):
     """Weights handed over in host memory as bfloat16, float32 or float64 (the same values) are
     converted by role: operands of products to the engine's type, norm weights to 32-bit."""
