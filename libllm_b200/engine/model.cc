@@ -175,17 +175,20 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
     const bool last = i + 1 == spec_.schedule.size();
     ctx.rows_read_after = last && ctx.n_want > 0 && ctx.n_want < ctx.n_tokens ? ctx.want_rows : nullptr;
     ctx.n_rows_read_after = ctx.rows_read_after ? ctx.n_want : 0;
+    ctx.nothing_read_after = last && ctx.n_want == 0;
     LayerCache lc;
     const bool has_cache = cache.layer_cache((int)i, e.cache_from, tables, table_width, &lc);
     StateView sv = cache.state_view((int)i);
     layers_[(size_t)e.layer]->forward(ctx, stream, has_cache ? &lc : nullptr, sv.empty() ? nullptr : &sv);
   }
   ctx.arena = step_arena;
+  ctx.nothing_read_after = false;
   if (ctx.n_want == 0) {
     flush_chain(ctx);
     return Act();
   }
   ctx.rows_read_after = nullptr;
+  ctx.nothing_read_after = false;
   Act h = stream.picked ? final_norm_->forward(ctx, stream) : final_norm_->forward(ctx, stream, ctx.want_rows, ctx.n_want);
   Act logits = linear(ctx, h, *head_, nullptr, DType::F32);
   flush_chain(ctx);

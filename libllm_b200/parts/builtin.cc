@@ -458,6 +458,11 @@ class PreNormBlock : public Block {
     Act r = mixer_->forward(ctx, h, cache, state);
     sink(false);
     stream.pending = r.data == (void *)stream.resid ? Act() : r;
+    if (ctx.nothing_read_after) {       // no logits wanted from this step: the stream is read by nobody
+      flush_chain(ctx);
+      stream.pending = Act();
+      return;
+    }
     if (ctx.rows_read_after && ctx.n_rows_read_after < stream.rows && !stream.picked) {
       // the last layer of a prompt step: the feed-forward of the wanted rows alone
       flush_chain(ctx);

@@ -132,6 +132,7 @@ struct StepContext {
   // (ResidualStream::picked); one that ignores it computes all rows as before.
   const int *rows_read_after = nullptr;
   int n_rows_read_after = 0;
+  bool nothing_read_after = false;   // the same with no row wanted at all (a piece of a long prompt): the mixer's cache writes are all that counts
 };
 
 // Device memory for a step's activations: handed out front to back, taken back all at once.

@@ -214,6 +214,14 @@ def test_a_prompt_whose_last_row_alone_is_wanted(name, dtype):
     check_logits(got[1:], ref_b[[40]], dtype, "b's next token")
     engine.close_sequence(sa)
     engine.close_sequence(sb)
+    # the same prompt cut into launch sequences of 48 tokens: the first six want nothing at all
+    engine, c, w = setup(name, dtype, max_step_tokens=48)
+    sa = engine.open_sequence()
+    got = torch.from_numpy(engine.step([StepItem(sa, a[:300], [299])]))
+    check_logits(got, ref_a[[299]], dtype, "last row of a, cut")
+    got = torch.from_numpy(engine.step([StepItem(sa, a[300:], [0])]))
+    check_logits(got, ref_a[[300]], dtype, "a's next token, cut")
+    engine.close_sequence(sa)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
