@@ -145,11 +145,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const unsigned dst = smem_u32(smem + (size_t)stage * S::STAGE_BYTES);
       if (leader) {
         mbar_expect_tx(bar_full + 8 * stage, S::STAGE_BYTES);
-        if (SW == 2) {                    // 128 gate rows, then 128 up rows
+        if (SW == 2) {                    // 128 gate rows, then 128 up rows: the map's boxes are 128 rows here
           tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
-          tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_a + 64, bar_full + 8 * stage);
           tma_load_2d(dst + TC_A_BYTES, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
-          tma_load_2d(dst + TC_A_BYTES + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b + 64, bar_full + 8 * stage);
         } else {
           tma_load_2d(dst, &map_w, w.kb * TC_BK, w.row_a, bar_full + 8 * stage);
           tma_load_2d(dst + TC_A_BYTES / 2, &map_w, w.kb * TC_BK, w.row_b, bar_full + 8 * stage);
@@ -332,7 +330,7 @@ int launch_tc(const void *x, long long ldx, const void *W, void *out, long long 
   const int kb_per_part = (n_kblocks + k_parts - 1) / k_parts;
   LLM_REQUIRE((long long)(k_parts - 1) * kb_per_part < n_kblocks, "gemm_tc: %d parts leave one of them without work (K = %d)", k_parts, K);
   CUtensorMap map_w, map_x;
-  int rc = get_map(W, N, K, K, 64, &map_w);
+  int rc = get_map(W, N, K, K, SW == 2 ? 128 : 64, &map_w);
   if (rc != LLM_OK) return rc;
   rc = get_map(x, M, K, ldx, TN, &map_x);
   if (rc != LLM_OK) return rc;
