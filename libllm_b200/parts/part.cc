@@ -24,7 +24,7 @@ void *Arena::alloc(size_t bytes, size_t align) {
     if (frozen_)
       LLM_THROW(Extension, "a captured step asked for more device memory (%zu bytes) than its first run", bytes);
     // at least as much again as is held: a step that needs gigabytes asks the driver a few times, not hundreds
-    chunks_.emplace_back(std::max({chunk_bytes_, bytes + align, reserved() / 2}));
+    chunks_.emplace_back(std::max({chunk_bytes_, bytes + align, std::min(reserved() / 2, (size_t)1 << 30)}));
   }
 }
 
