@@ -25,3 +25,21 @@ def test_reference_arm_says_why_it_is_unavailable():
     assert p.returncode == 0
     rec = json.loads(p.stdout.strip().splitlines()[-1])
     assert rec["impl"] == "reference" and isinstance(rec["unavailable"], str) and "\n" not in rec["unavailable"]
+
+
+def test_bytes_and_flops_the_roofline_fractions_rest_on():
+    """The step's bytes and the prompt's flops for the benchmark's sizes, against the figures worked
+    out by hand: 1,235,814,400 parameters at 2 bytes, 32,768 bytes of cache a token, and the products of
+    a 2,048-token prompt with the last layer's feed-forward and the output matrix for one row only."""
+    sys.path.insert(0, ROOT)
+    import bench
+    weight_bytes, kv_per_token, flops = bench.model_numbers(bench.LLAMA_1B)
+    assert weight_bytes == 2 * 1_235_814_400
+    assert kv_per_token == 2 * 16 * 8 * 64 * 2
+    H, I, L, V, T = 2048, 8192, 16, 128256, 2048
+    linear = 2 * T * L * (H * 3072 + H * H) + 2 * (T * (L - 1) + 1) * 3 * H * I
+    attention = L * 4 * 32 * 64 * T * (T + 1) // 2
+    assert flops(T) == linear + attention + 2 * V * H
+    assert abs(flops(T) / 1e12 - 4.055) < 0.001
+    w8, kv8, _ = bench.model_numbers(bench.LLAMA_8B)
+    assert kv8 == 131072 and abs(w8 / 1e9 - 15.009) < 0.06      # the 8B model: layers, output matrix and norms (no token table)
