@@ -292,13 +292,13 @@ def bench_chain_layer(args, timer):
 def bench_add_rmsnorm(args, timer):
     import torch
     from ..csrc import ops
-    T, H = args.m, args.hidden
+    T, H, P = args.m, args.hidden, max(1, args.parts)
     resid = torch.randn(T, H, device="cuda")
-    delta = torch.randn(T, H, device="cuda")
+    delta = torch.randn(T, H, device="cuda") if P == 1 else torch.randn(P, T, H, device="cuda")
     w = torch.ones(H, device="cuda")
     out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
     us = timer.run(lambda: ops.add_rmsnorm(resid, delta, w, 1e-5, out))
-    report("add_rmsnorm", us, bytes_moved=T * H * (4 + 4 + 4 + 2), m=T, hidden=H)
+    report("add_rmsnorm", us, bytes_moved=T * H * (4 + 4 * P + 4 + 2), m=T, hidden=H, parts=P)
 
 
 def bench_sampling(args, timer):
@@ -336,6 +336,7 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=128256)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--parts", type=int, default=1, help="add_rmsnorm: partial products the norm adds up first")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
