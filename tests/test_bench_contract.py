@@ -43,3 +43,29 @@ def test_bytes_and_flops_the_roofline_fractions_rest_on():
     assert abs(flops(T) / 1e12 - 4.055) < 0.001
     w8, kv8, _ = bench.model_numbers(bench.LLAMA_8B)
     assert kv8 == 131072 and abs(w8 / 1e9 - 15.009) < 0.06      # the 8B model: layers, output matrix and norms (no token table)
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_the_benchmark_line_on_a_gpu():
+    """One short run of the benchmark itself: one JSON line with the keys the contract names, launches
+    counted, both timings of the step, and fractions that are fractions."""
+    p = run("--steps", "8", "--warmup", "3", "--no-points")
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "ms_per_step_median", "higher_is_better",
+                "scaling", "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "clocks", "prefill", "roofline",
+                "points", "dominant_kernel"):
+        assert key in rec, key
+    assert rec["n_gpus"] == 1 and rec["steps"] == 8 and rec["dtype"] == "bf16" and rec["higher_is_better"] is True
+    assert len(rec["config"]) <= 20 and all(not isinstance(v, (dict, list)) for v in rec["config"].values())
+    assert rec["config"]["layers"] == rec["config"]["layers_full"] == 16 and rec["config"]["global_batch"] == 8
+    assert rec["gpu_launches"] >= 8 * 100
+    assert abs(rec["value"] - 8 * 1000.0 / rec["ms_per_step"]) < 1.0
+    assert 0 < rec["e2e"]["value"] <= rec["value"] * 1.05 and rec["e2e"]["h2d_bytes_per_step"] > 0 and rec["e2e"]["d2h_bytes_per_step"] > 0
+    assert 0.2 < rec["roofline"]["frac"] < 1.1 and 0.2 < rec["prefill"]["frac"] < 1.1 and rec["prefill"]["tokens"] == 2048
+    assert 0.2 < rec["dominant_kernel"]["frac"] < 1.1
